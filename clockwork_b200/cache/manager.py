@@ -172,7 +172,7 @@ class CacheManager:
             raise ValueError(f"request {request_id!r} already holds cache")
         req = RequestCache(request_id, [[] for _ in self.groups], live_from=[0] * len(self.groups))
         if shared_prefix:
-            if len(self.groups) != 1 or self.groups[0].need.window is not None or self.state.needs:
+            if len(self.groups) != 1 or self.groups[0].need.window is not None or self.groups[0].need.block is not None or self.state.needs:
                 raise ValueError("shared prefixes need a single group of full-attention layers")
             req.tables[0] = list(shared_prefix)
             req.shared_prefix_pages = len(shared_prefix)
@@ -266,13 +266,18 @@ class CacheManager:
 
     def release_behind_window(self, req: RequestCache, computed: int) -> int:
         """Give back pages of windowed groups that no later token can read: a query at position
-        p >= computed reads keys in [p + 1 - window, p] only.  Returns the number given back."""
+        p >= computed reads keys in [p + 1 - window, p] only; in a group whose layers read blocks of positions,
+        keys from the start of p's own block on.  Returns the number given back."""
         given = 0
         for g, group in enumerate(self.groups):
-            window = group.need.window
-            if window is None:
+            window, block = group.need.window, group.need.block
+            if window is None and block is None:
                 continue
-            first_needed = max(0, computed + 1 - window)
+            first_needed = 0
+            if window is not None:
+                first_needed = max(0, computed + 1 - window)
+            if block is not None:
+                first_needed = max(first_needed, computed - computed % block)
             keep_from = first_needed // self.page_size
             table = req.tables[g]
             for blk in range(req.live_from[g], min(keep_from, len(table))):

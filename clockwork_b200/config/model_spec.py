@@ -12,7 +12,9 @@ A spec is plain data:
   Different layers may use different kinds and sizes.
 * ``schedule`` is the order in which layers run.  An entry may name a layer twice, or let
   a layer read the cache that another layer wrote (``cache_layer`` differs from ``layer``
-  and ``write_cache`` is false).
+  and ``write_cache`` is false).  A cache layer is just a number: a layer that runs several
+  times with a cache or state of its own each time names a fresh number (at or above the
+  number of layers) for every further pass (``looped_schedule``).
 """
 
 from __future__ import annotations
@@ -74,6 +76,7 @@ class ModelSpec:
     eos_token_ids: tuple[int, ...] = ()
     max_position_embeddings: int | None = None
     embedding_scale: float = 1.0  # the embedding rows are multiplied by this (the output head, if tied, is not)
+    logit_softcap: float | None = None  # logits <- cap * tanh(logits / cap)
     absolute_positions: PartSpec | None = None  # a position part that adds a vector per position to the embedding
     raw: dict[str, Any] = field(default_factory=dict)  # the config.json it came from
 
@@ -82,12 +85,14 @@ class ModelSpec:
             raise ValueError("vocab_size and hidden_size must be positive")
         if not self.layers:
             raise ValueError("a model needs at least one layer")
+        if self.logit_softcap is not None and not self.logit_softcap > 0:
+            raise ValueError("logit_softcap must be positive")
         writers: set[int] = set()
         for step in self.schedule:
             if not 0 <= step.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {step.layer}, model has {len(self.layers)}")
             cache_layer = step.resolved_cache_layer()
-            if not 0 <= cache_layer < len(self.layers):
+            if cache_layer < 0:
                 raise ValueError(f"schedule names cache layer {cache_layer}")
             if step.write_cache:
                 writers.add(cache_layer)
@@ -99,3 +104,17 @@ class ModelSpec:
 
 def sequential_schedule(num_layers: int) -> list[ExecStep]:
     return [ExecStep(layer=i) for i in range(num_layers)]
+
+
+def looped_schedule(num_layers: int, start: int, stop: int, times: int) -> list[ExecStep]:
+    """Layers 0 .. start-1 once, layers start .. stop-1 ``times`` times in a row with the same weights, then the rest.
+    Every pass keeps a cache or state of its own: the first pass under the layer's own number, pass p > 0 of layer i under
+    ``num_layers + (p - 1) * (stop - start) + (i - start)``."""
+    if not 0 <= start <= stop <= num_layers or times < 1:
+        raise ValueError(f"a loop over layers {start} .. {stop - 1}, {times} times, does not fit {num_layers} layers")
+    steps = [ExecStep(layer=i) for i in range(start)]
+    for p in range(times):
+        for i in range(start, stop):
+            steps.append(ExecStep(layer=i, cache_layer=i if p == 0 else num_layers + (p - 1) * (stop - start) + (i - start)))
+    steps.extend(ExecStep(layer=i) for i in range(stop, num_layers))
+    return steps

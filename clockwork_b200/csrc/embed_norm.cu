@@ -8,7 +8,7 @@
 
 template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table,
-                             const int* __restrict__ ids, int H, int V, int* status) {
+                             const int* __restrict__ ids, int H, int V, float scale, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x;
@@ -20,18 +20,18 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
         return;
     }
     const T* src = table + (size_t)id * H;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = to_f(src[c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) o[c] = to_f(src[c]) * scale;  // (scale 1: the row as it is)
 }
 
 extern "C" int cw_embed(float* out, const void* table, const int* ids, int N, int H, int V,
-                        int dtype, int* status, cudaStream_t stream) {
+                        int dtype, float scale, int* status, cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || H <= 0 || V <= 0) return CW_ERR_BAD_SIZE;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == 0)
-        return cw_launch(embed_kernel<float>, dim3(N), dim3(threads), 0, stream, 1, out, (const float*)table, ids, H, V, status);
+        return cw_launch(embed_kernel<float>, dim3(N), dim3(threads), 0, stream, 1, out, (const float*)table, ids, H, V, scale, status);
     if (dtype == 1)
-        return cw_launch(embed_kernel<bf16>, dim3(N), dim3(threads), 0, stream, 1, out, (const bf16*)table, ids, H, V, status);
+        return cw_launch(embed_kernel<bf16>, dim3(N), dim3(threads), 0, stream, 1, out, (const bf16*)table, ids, H, V, scale, status);
     return CW_ERR_BAD_DTYPE;
 }
 
@@ -361,6 +361,51 @@ extern "C" int cw_pair_rmsnorm_add(float* resid, const float* a, const float* b,
     if (N == 0) return CW_OK;
     if (N < 0 || W <= 0) return CW_ERR_BAD_SIZE;
     return cw_launch_ordered(pair_rmsnorm_add_kernel, dim3(N), dim3(256), 0, stream, resid, a, b, wa, wb, eps, factor, W);
+}
+
+// ---- a weighted sum of contributions, normed over the width, into the residual ------------------------
+// y = ca a (+ cb b);  resid[row] += y / sqrt(mean(y^2) + eps) * w, everything float32 (b may be null).
+__global__ void __launch_bounds__(256)
+sum_rmsnorm_add_kernel(float* __restrict__ resid, const float* __restrict__ a, const float* __restrict__ b, float ca, float cb,
+                       const float* __restrict__ w, float eps, int W) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t at = (size_t)blockIdx.x * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float y = b != nullptr ? fmaf(cb, b[at + c], ca * a[at + c]) : ca * a[at + c];
+        ss = fmaf(y, y, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float y = b != nullptr ? fmaf(cb, b[at + c], ca * a[at + c]) : ca * a[at + c];
+        resid[at + c] += y * inv * w[c];
+    }
+}
+
+extern "C" int cw_sum_rmsnorm_add(float* resid, const float* a, const float* b, float ca, float cb, const float* w, float eps,
+                                  int N, int W, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || W <= 0 || a == nullptr) return CW_ERR_BAD_SIZE;
+    int threads = 64;
+    while (threads < 256 && threads * 4 < W) threads *= 2;
+    return cw_launch_ordered(sum_rmsnorm_add_kernel, dim3(N), dim3(threads), 0, stream, resid, a, b, ca, cb, w, eps, W);
+}
+
+// ---- logits bent towards a bound ------------------------------------------------------------------------
+// x <- cap tanh(x / cap), in place, float32.
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int cw_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n == 0) return CW_OK;
+    if (n < 0 || !(cap > 0.f)) return CW_ERR_BAD_SIZE;
+    const int blocks = (int)min((long long)148 * 8, (n + 255) / 256);
+    return cw_launch_ordered(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, n, cap);
 }
 
 static int g_pdl = 1;

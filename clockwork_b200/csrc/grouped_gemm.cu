@@ -8,8 +8,9 @@
 // float32 accumulation in k order on the CUDA cores in both run precisions: a row's result depends on
 // the row and its group only, never on which other rows share its tile.
 //
-// Beside it the router of a mixture of experts (float32 logits, the `top` largest, softmax over the
-// chosen), the grouping of (token, choice) pairs by expert, and the weighted sum of the experts'
+// Beside it the router of a mixture of experts (float32 logits, the `top` largest, weighted by the softmax
+// over the chosen or by their shares of the softmax over all; optionally only experts of the best runs of
+// neighbours), the grouping of (token, choice) pairs by expert, and the weighted sum of the experts'
 // outputs into the float32 residual, in choice order.
 #include "common.cuh"
 
@@ -19,8 +20,19 @@
 
 #define GG_EPI_STORE 0        // C (T) = acc
 #define GG_EPI_STORE_F32 1    // C (float) = acc
-#define GG_EPI_SILU_MUL 2     // C (T) = silu(acc) * acc2, acc2 from B2
+#define GG_EPI_SILU_MUL 2     // C (T) = silu(acc) * acc2, acc2 from B2; with a positive `glu_limit` the clamped form below
 #define GG_EPI_SIGMOID_GATE 3 // C (T) = acc * sigmoid(gate[dst, c_group_off*g + n])
+
+// The gated activation of the two-product form: silu(a) b, or, with a positive limit,
+//   a' = min(a, limit), b' = clamp(b, -limit, limit):  a' sigmoid(1.702 a') (b' + 1)
+__device__ __forceinline__ float gg_glu(float a, float b, float limit) {
+    if (limit > 0.f) {
+        a = fminf(a, limit);
+        b = fminf(fmaxf(b, -limit), limit);
+        return a / (1.f + expf(-1.702f * a)) * (b + 1.f);
+    }
+    return a / (1.f + expf(-a)) * b;
+}
 
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
@@ -28,7 +40,7 @@ grouped_gemm_kernel(const T* __restrict__ A, int lda, int a_group_off, const T* 
                     long long b_stride, void* __restrict__ Cv, int ldc, int c_group_off,
                     const int* __restrict__ offsets, const int* __restrict__ a_index, int a_div,
                     const int* __restrict__ c_index, const T* __restrict__ gate, int ldg,
-                    int M, int Nout, int K, int G) {
+                    int M, int Nout, int K, int G, float glu_limit) {
     __shared__ float As[GG_TK][GG_TM + 1];
     __shared__ float Bs[GG_TK][GG_TN + 1];
     __shared__ float B2s[EPI == GG_EPI_SILU_MUL ? GG_TK : 1][GG_TN + 1];
@@ -115,7 +127,7 @@ grouped_gemm_kernel(const T* __restrict__ A, int lda, int a_group_off, const T* 
             if (EPI == GG_EPI_STORE_F32) {
                 ((float*)Cv)[at] = v;
             } else {
-                if (EPI == GG_EPI_SILU_MUL) v = v / (1.f + expf(-v)) * acc2[r][c];
+                if (EPI == GG_EPI_SILU_MUL) v = gg_glu(v, acc2[r][c], glu_limit);
                 if (EPI == GG_EPI_SIGMOID_GATE) v = v / (1.f + expf(-to_f(gate[(size_t)d * ldg + (size_t)g * c_group_off + n])));
                 ((T*)Cv)[at] = from_f<T>(v);
             }
@@ -155,7 +167,7 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ A, int lda, int a_group_off, co
                         const bf16* __restrict__ B2, long long b_stride, void* __restrict__ Cv, int ldc, int c_group_off,
                         const int* __restrict__ offsets, const int* __restrict__ a_index, int a_div,
                         const int* __restrict__ c_index, const bf16* __restrict__ gate, int ldg,
-                        int M, int Nout, int K, int G) {
+                        int M, int Nout, int K, int G, float glu_limit) {
     extern __shared__ __align__(16) unsigned char gm_smem[];
     constexpr bool TWO = EPI == GG_EPI_SILU_MUL;
     bf16* As = (bf16*)gm_smem;                       // [stages][TM][LD]
@@ -278,7 +290,7 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ A, int lda, int a_group_off, co
                     if (EPI == GG_EPI_STORE_F32) {
                         ((float*)Cv)[at] = v;
                     } else {
-                        if (TWO) v = v / (1.f + expf(-v)) * acc2[TWO ? mi : 0][TWO ? ni : 0][half * 2 + e];
+                        if (TWO) v = gg_glu(v, acc2[TWO ? mi : 0][TWO ? ni : 0][half * 2 + e], glu_limit);
                         if (EPI == GG_EPI_SIGMOID_GATE)
                             v = v / (1.f + expf(-to_f(gate[(size_t)d * ldg + (size_t)g * c_group_off + n])));
                         ((bf16*)Cv)[at] = __float2bfloat16_rn(v);
@@ -292,7 +304,7 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ A, int lda, int a_group_off, co
 template <int EPI>
 static int launch_grouped_mma(dim3 grid, cudaStream_t stream, const void* A, int lda, int a_group_off, const void* B, const void* B2,
                               long long b_stride, void* C, int ldc, int c_group_off, const int* offsets, const int* a_index,
-                              int a_div, const int* c_index, const void* gate, int ldg, int M, int Nout, int K, int G) {
+                              int a_div, const int* c_index, const void* gate, int ldg, int M, int Nout, int K, int G, float glu_limit) {
     const size_t smem = (size_t)GM_STAGES * (GM_TM + (EPI == GG_EPI_SILU_MUL ? 2 : 1) * GM_TN) * GM_LD * sizeof(bf16);
     static bool configured = false;  // (per instantiation)
     if (!configured) {
@@ -302,7 +314,7 @@ static int launch_grouped_mma(dim3 grid, cudaStream_t stream, const void* A, int
     }
     return cw_launch_ordered(grouped_gemm_mma_kernel<EPI>, grid, dim3(256), smem, stream, (const bf16*)A, lda, a_group_off, (const bf16*)B,
                      (const bf16*)B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, c_index, (const bf16*)gate, ldg, M, Nout,
-                     K, G);
+                     K, G, glu_limit);
 }
 
 static int g_grouped_mma = 1;
@@ -312,11 +324,11 @@ template <typename T>
 static int launch_grouped(int epi, dim3 grid, cudaStream_t stream, const void* A, int lda, int a_group_off, const void* B,
                           const void* B2, long long b_stride, void* C, int ldc, int c_group_off, const int* offsets,
                           const int* a_index, int a_div, const int* c_index, const void* gate, int ldg, int M, int Nout, int K,
-                          int G) {
+                          int G, float glu_limit) {
 #define GG_GO(E)                                                                                                              \
     return cw_launch_ordered(grouped_gemm_kernel<T, E>, grid, dim3(256), 0, stream, (const T*)A, lda, a_group_off, (const T*)B,    \
                      (const T*)B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, c_index, (const T*)gate, ldg, M,   \
-                     Nout, K, G)
+                     Nout, K, G, glu_limit)
     switch (epi) {
         case GG_EPI_STORE: GG_GO(GG_EPI_STORE);
         case GG_EPI_STORE_F32: GG_GO(GG_EPI_STORE_F32);
@@ -333,7 +345,7 @@ static int launch_grouped(int epi, dim3 grid, cudaStream_t stream, const void* A
 extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const void* B, const void* B2, long long b_stride,
                                void* C, int ldc, int c_group_off, const int* offsets, const int* a_index, int a_div,
                                const int* c_index, const void* gate, int ldg, int M, int Nout, int K, int G, int epilogue,
-                               int dtype, cudaStream_t stream) {
+                               float glu_limit, int dtype, cudaStream_t stream) {
     if (M == 0) return CW_OK;
     if (M < 0 || Nout <= 0 || K <= 0 || G <= 0 || a_div <= 0) return CW_ERR_BAD_SIZE;
     if (epilogue == GG_EPI_SILU_MUL && B2 == nullptr) return CW_ERR_BAD_SIZE;
@@ -343,7 +355,7 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
     dim3 grid((unsigned)tiles, (Nout + GG_TN - 1) / GG_TN);
     if (dtype == 0)
         return launch_grouped<float>(epilogue, grid, stream, A, lda, a_group_off, B, B2, b_stride, C, ldc, c_group_off, offsets,
-                                     a_index, a_div, c_index, gate, ldg, M, Nout, K, G);
+                                     a_index, a_div, c_index, gate, ldg, M, Nout, K, G, glu_limit);
     const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_group_off % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)B & 15) == 0 &&
                          ((uintptr_t)B2 & 15) == 0;
     if (dtype == 1 && g_grouped_mma && aligned) {
@@ -351,7 +363,7 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
         dim3 mgrid((unsigned)mtiles, (Nout + GM_TN - 1) / GM_TN);
 #define GM_GO(E)                                                                                                                 \
     return launch_grouped_mma<E>(mgrid, stream, A, lda, a_group_off, B, B2, b_stride, C, ldc, c_group_off, offsets, a_index, a_div, \
-                                 c_index, gate, ldg, M, Nout, K, G)
+                                 c_index, gate, ldg, M, Nout, K, G, glu_limit)
         switch (epilogue) {
             case GG_EPI_STORE: GM_GO(GG_EPI_STORE);
             case GG_EPI_STORE_F32: GM_GO(GG_EPI_STORE_F32);
@@ -363,18 +375,21 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
     }
     if (dtype == 1)
         return launch_grouped<bf16>(epilogue, grid, stream, A, lda, a_group_off, B, B2, b_stride, C, ldc, c_group_off, offsets,
-                                    a_index, a_div, c_index, gate, ldg, M, Nout, K, G);
+                                    a_index, a_div, c_index, gate, ldg, M, Nout, K, G, glu_limit);
     return CW_ERR_BAD_DTYPE;
 }
 
 // ---- router ---------------------------------------------------------------------------------------
 // logits [N, E] float32 (a product with float32 accumulation, made by the caller) + bias; the `top`
-// largest (the lower index wins a tie); weights = softmax over the chosen logits.  sel < 0 marks a
-// padding row.  A warp per token.
+// largest (the lower index wins a tie).  sel < 0 marks a padding row.  A warp per token.
+//   mode 0: weights = softmax over the chosen logits.
+//   mode 1: scores = softmax over all E logits; weights = the chosen experts' scores as they are.
+// groups > 1: the experts lie in `groups` equal runs of neighbours; a run counts as its largest entry, and
+// only experts of the `keep` best runs can be chosen.
 __global__ void __launch_bounds__(128)
 moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b, const int* __restrict__ tok_seq,
-                  int* __restrict__ sel, float* __restrict__ wt, int N, int E, int top) {
-    extern __shared__ float choose_s[];  // per warp: [E] logits, then [top] chosen logits
+                  int* __restrict__ sel, float* __restrict__ wt, int N, int E, int top, int mode, int groups, int keep) {
+    extern __shared__ float choose_s[];  // per warp: [E] logits or scores, [top] chosen ones, [groups] the runs' best
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * 4 + warp;
@@ -386,10 +401,48 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b,
         }
         return;
     }
-    float* logit_s = choose_s + (size_t)warp * (E + top);
+    float* logit_s = choose_s + (size_t)warp * (E + top + groups);
     float* chosen_s = logit_s + E;
+    float* group_s = chosen_s + top;
     for (int e = lane; e < E; e += 32) logit_s[e] = logits[(size_t)row * E + e] + (b != nullptr ? b[e] : 0.f);
     __syncwarp();
+    if (mode == 1) {  // every expert's share of the softmax over all of them (sums in a fixed order)
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logit_s[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(logit_s[e] - mx);
+        sum = warp_sum(sum);
+        for (int e = lane; e < E; e += 32) logit_s[e] = expf(logit_s[e] - mx) / sum;
+        __syncwarp();
+    }
+    if (groups > 1) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float best = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, logit_s[e]);
+            group_s[g] = best;
+        }
+        __syncwarp();
+        for (int t = 0; t < keep; ++t) {  // the best runs one by one; a kept run is marked with +inf
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32) {
+                const float v = group_s[g];
+                if (v != INFINITY && v > best) best = v, at = g;
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
+            }
+            if (lane == 0 && at != 0x7fffffff) group_s[at] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (group_s[e / per] != INFINITY) logit_s[e] = -INFINITY;
+        __syncwarp();
+    }
     for (int t = 0; t < top; ++t) {
         float best = -INFINITY;
         int at = 0x7fffffff;
@@ -402,13 +455,17 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b,
             const int oa = __shfl_xor_sync(0xffffffffu, at, o);
             if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
         }
-        if (at == 0x7fffffff) at = t % E;  // no finite logit left (never with finite inputs)
+        if (at == 0x7fffffff) at = t % E;  // no finite entry left (never with finite inputs and enough allowed experts)
         if (lane == 0) {
             sel[(size_t)row * top + t] = at;
             chosen_s[t] = best;
             logit_s[at] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (mode == 1) {
+        for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = chosen_s[t] == -INFINITY ? 0.f : chosen_s[t];
+        return;
     }
     const float first = chosen_s[0];
     float total = 0.f;
@@ -417,12 +474,14 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b,
 }
 
 extern "C" int cw_moe_choose(const float* logits, const float* b, const int* tok_seq, int* sel, float* wt, int N, int E, int top,
-                             cudaStream_t stream) {
+                             int mode, int groups, int keep, cudaStream_t stream) {
     if (N == 0) return CW_OK;
-    if (N < 0 || E <= 0 || top <= 0 || top > E) return CW_ERR_BAD_SIZE;
-    const size_t smem = 4 * (size_t)(E + top) * sizeof(float);
+    if (N < 0 || E <= 0 || top <= 0 || top > E || mode < 0 || mode > 1) return CW_ERR_BAD_SIZE;
+    if (groups < 1 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top) return CW_ERR_BAD_SIZE;
+    const size_t smem = 4 * (size_t)(E + top + groups) * sizeof(float);
     if (smem > (48 << 10)) return CW_ERR_UNSUPPORTED;
-    return cw_launch_ordered(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, logits, b, tok_seq, sel, wt, N, E, top);
+    return cw_launch_ordered(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, logits, b, tok_seq, sel, wt, N, E, top,
+                             mode, groups, keep);
 }
 
 // ---- pairs by expert --------------------------------------------------------------------------------

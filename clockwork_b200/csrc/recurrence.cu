@@ -145,7 +145,11 @@ extern "C" int cw_carry_rows(const void* x, int ldx, float* state, long long sta
 //       S_ij <- a_i S_ij + k_i v_j;  y_j = q_scale sum_i q_i S_ij                   (coef = a [N, H*Dk])
 //   FORM 3 (one constant decay per head, output after the update):
 //       S_ij <- p0_h S_ij + k_i v_j;  y_j = q_scale sum_i q_i S_ij                  (no coefficients)
-// with the coefficients from cw_recurrence_coefficients (forms 0 and 1) or cw_sigmoid_power_decay (form 2).
+//   FORM 4 (form 1 without the skip term, its coefficients made elsewhere, and one more value column than v has,
+//           whose input is 1 for every token: that column of S is the decayed sum of the scaled keys):
+//       S_ij <- a S_ij + b k_i v_j;  y_j = q_scale sum_i q_i S_ij,  v_(Dv-1) = 1     (coef = [a | b] [N, >= 2H]; v [N, H*(Dv-1)])
+// with the coefficients from cw_recurrence_coefficients (forms 0 and 1), cw_sigmoid_power_decay (form 2) or
+// cw_gate_scan (form 4).
 // q and k of head h are those of group h / heads_per_group.  Blocks: (request, head, slice of value columns).
 // What the recurrence multiplies by, computed once per token before the scan (float32):
 //   FORM 0: a[t, c] = exp(-exp(pre[t, c] + p0[c])) for the H*Dk channels, in place
@@ -218,7 +222,8 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     }
     // one buffer: q [RC][Dk], k [RC][Dk], a [RC][Dk] (forms 0 and 2) or a, dt [2][RC] (FORM 1) or nothing (FORM 3), v [RC][JB]
     constexpr bool CH = FORM == 0 || FORM == 2;  // a decay per key channel and token
-    const int a_words = CH ? RC * Dk : (FORM == 1 ? 2 * RC : 0);
+    constexpr bool HD = FORM == 1 || FORM == 4;  // a decay and an input scale per head and token
+    const int a_words = CH ? RC * Dk : (HD ? 2 * RC : 0);
     const int buf_words = 2 * RC * Dk + a_words + RC * JB;
     const int g = h / heads_per_group;
     float* S_mem = state + slots[seq] * state_stride + state_off + ((size_t)h * Dv + (live ? j : 0)) * Dk;
@@ -239,9 +244,10 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
     const float head_decay = FORM == 3 ? p0[h] : 0.f;
     const float* qp = q + (size_t)g * Dk;
     const float* kp = k + (size_t)g * Dk;
-    const float* pp = CH ? pre + (size_t)h * Dk : (FORM == 1 ? pre + h : nullptr);
-    const float* vp = v + (size_t)h * Dv + j0;
-    const int nv = min(JB, Dv - j0);
+    const float* pp = CH ? pre + (size_t)h * Dk : (HD ? pre + h : nullptr);
+    const int Dvin = FORM == 4 ? Dv - 1 : Dv;  // value columns that v holds
+    const float* vp = v + (size_t)h * Dvin + j0;
+    const int nv = min(JB, Dvin - j0);
     auto fetch = [&](int t0, float* buf) {  // raw operands of tokens t0 .. t0+RC-1 (those below `end`)
         const int n = min(RC, end - t0);
         float* qs = buf;
@@ -265,7 +271,7 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
                 if (CH) cp_async4(as + idx, pp + (size_t)(t0 + t) * ldp + i);
             }
         }
-        if (FORM == 1)
+        if (HD)
             for (int t = tid; t < 2 * n; t += blockDim.x) {  // a and dt of the head
                 const int tok = t >> 1, second = t & 1;
                 cp_async4(as + second * RC + tok, pp + (size_t)(t0 + tok) * ldp + second * H);
@@ -293,9 +299,9 @@ recurrence_scan_kernel(const float* __restrict__ q, int ldq, const float* __rest
         for (int t = 0; t < RC; ++t) {
             part[t] = 0.f;
             if (t < n) {
-                const float vraw = live ? vs[t * JB + jl] : 0.f;
-                const float a1 = FORM == 1 ? as[t] : head_decay;
-                const float vc = FORM == 1 ? vraw * as[RC + t] : vraw;  // the step size scales the update
+                const float vraw = live ? ((FORM == 4 && j == Dv - 1) ? 1.f : vs[t * JB + jl]) : 0.f;
+                const float a1 = HD ? as[t] : head_decay;
+                const float vc = HD ? vraw * as[RC + t] : vraw;  // the step size scales the update
                 float sum = 0.f;
                 if (VEC) {
                     const int at = t * Dk + ipart * 4, up = at + half;
@@ -376,21 +382,23 @@ extern "C" int cw_recurrence_scan(int form, const float* q, int ldq, const float
     while (threads > 32 && threads / IP >= 2 * Dv) threads /= 2;
     const int JB = threads / IP;
     dim3 grid(S, H, (Dv + JB - 1) / JB);
-    if (form < 0 || form > 3) return CW_ERR_UNSUPPORTED;
+    if (form < 0 || form > 4) return CW_ERR_UNSUPPORTED;
+    if (form == 4 && Dv < 2) return CW_ERR_BAD_SIZE;
     const bool ch = form == 0 || form == 2;  // coefficients per key channel
     if ((form != 3 && pre == nullptr) || (form == 3 && p0 == nullptr)) return CW_ERR_BAD_SIZE;
     const int wide = Dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (!ch || ldp % 4 == 0) && ((uintptr_t)q & 15) == 0 &&
                      ((uintptr_t)k & 15) == 0 && (!ch || ((uintptr_t)pre & 15) == 0);
-    const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (ch ? RC * Dk : (form == 1 ? 2 * RC : 0)) + RC * JB);
+    const size_t smem = 2 * sizeof(float) * (size_t)(2 * RC * Dk + (ch ? RC * Dk : (form == 1 || form == 4 ? 2 * RC : 0)) + RC * JB);
     const bool vec = wide && Dk == IP * RS;
     const int which = form * 2 + (vec ? 1 : 0);
-    static size_t allowed[8] = {48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10};
+    static size_t allowed[10] = {48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10, 48 << 10};
     using Kernel = void (*)(const float*, int, const float*, int, const float*, int, const float*, int, const float*, const float*,
                             const float*, float*, long long, long long, const long long*, const int*, const int*, int, int, int, int, int, int,
                             float*, int, float);
-    const Kernel kernels[8] = {recurrence_scan_kernel<0, false>, recurrence_scan_kernel<0, true>, recurrence_scan_kernel<1, false>,
-                               recurrence_scan_kernel<1, true>, recurrence_scan_kernel<2, false>, recurrence_scan_kernel<2, true>,
-                               recurrence_scan_kernel<3, false>, recurrence_scan_kernel<3, true>};
+    const Kernel kernels[10] = {recurrence_scan_kernel<0, false>, recurrence_scan_kernel<0, true>, recurrence_scan_kernel<1, false>,
+                                recurrence_scan_kernel<1, true>, recurrence_scan_kernel<2, false>, recurrence_scan_kernel<2, true>,
+                                recurrence_scan_kernel<3, false>, recurrence_scan_kernel<3, true>, recurrence_scan_kernel<4, false>,
+                                recurrence_scan_kernel<4, true>};
     if (smem > allowed[which]) {
         const cudaError_t e = cudaFuncSetAttribute(kernels[which], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;

@@ -10,6 +10,11 @@
 //   cw_window_attention  one flat batch of prompt portions and single tokens; a block per (token, part of its
 //                        window); query head h reads key/value head h / (H / G); position p sees positions
 //                        max(0, p - window + 1) .. p, all of which are in the cache when the kernel runs
+//                        (`blocked`: positions are cut into blocks of `window` instead, and p sees the positions
+//                        of its own block up to itself; `sink`: a logit per head that enters the softmax's
+//                        denominator once, with no key and no value)
+//   cw_rotate_store      turns the leading entries of every query and key head by the token's position (entry i with
+//                        entry i + dims/2), writes the queries out and the rows [key | value] into the cache
 //   (window_merge_kernel adds up the parts of a token's window; only launched when windows are cut)
 // bfloat16 calls run the tensor-core form further down when it takes the sizes; the CUDA-core kernel is the float32
 // path and the fallback.
@@ -53,6 +58,67 @@ extern "C" int cw_store_rows(const void* src, int ld, int col0, int width, void*
     return CW_ERR_BAD_DTYPE;
 }
 
+// src [N, ld] float32: a token's product row [queries (H*dk) | per key/value head: key (dk), value (dv)].  The first
+// `rot` entries of every query and key head are rotated: the pair (entry i, entry i + rot/2) by the angle
+// position * inv_freq[i], in float32.  Queries go to q_out [N, H*dk], the rows [key | value] to the cache row that the
+// token's slot names (slots null or < 0: nothing is stored).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotate_store_kernel(const float* __restrict__ src, int ld, const int* __restrict__ positions, const int* __restrict__ tok_seq,
+                    const int* __restrict__ slots, const float* __restrict__ inv_freq, int H, int G, int dk, int dv, int rot,
+                    T* __restrict__ q_out, T* __restrict__ cache, long long total_rows, int* __restrict__ status) {
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int HQ = H * dk, row = dk + dv, half = rot >> 1;
+    T* qo = q_out + (size_t)n * HQ;
+    if (tok_seq[n] < 0) {  // padding of a fixed-shape step
+        for (int c = threadIdx.x; c < HQ; c += blockDim.x) qo[c] = from_f<T>(0.f);
+        return;
+    }
+    const float p = (float)positions[n];
+    const float* x = src + (size_t)n * ld;
+    auto turned = [&](const float* head, int i) {  // entry i (< rot) of a head after the rotation
+        const int j = i < half ? i : i - half;
+        float sn, cs;
+        sincosf(p * inv_freq[j], &sn, &cs);
+        return i < half ? head[i] * cs - head[i + half] * sn : head[i] * cs + head[i - half] * sn;
+    };
+    for (int c = threadIdx.x; c < HQ; c += blockDim.x) {
+        const int h = c / dk, i = c - h * dk;
+        qo[c] = from_f<T>(i < rot ? turned(x + (size_t)h * dk, i) : x[c]);
+    }
+    const int slot = slots != nullptr ? slots[n] : -1;
+    if (slot < 0) return;
+    if (slot >= total_rows) {
+        if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, n, slot);
+        return;
+    }
+    T* to = cache + (size_t)slot * G * row;
+    const float* kv = x + HQ;
+    for (int c = threadIdx.x; c < G * row; c += blockDim.x) {
+        const int g = c / row, i = c - g * row;
+        to[c] = from_f<T>(i < rot ? turned(kv + (size_t)g * row, i) : kv[c]);
+    }
+}
+
+extern "C" int cw_rotate_store(const float* src, int ld, const int* positions, const int* tok_seq, const int* slots,
+                               const float* inv_freq, int N, int H, int G, int dk, int dv, int rot, void* q_out, void* cache,
+                               long long total_rows, int dtype, int* status, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || rot < 0 || rot > dk || (rot & 1) || ld < H * dk + G * (dk + dv) ||
+        (rot > 0 && inv_freq == nullptr) || total_rows < 0)
+        return CW_ERR_BAD_SIZE;
+    int threads = 64;
+    while (threads < 256 && threads < H * dk) threads *= 2;
+    if (dtype == 0)
+        return cw_launch_ordered(rotate_store_kernel<float>, dim3(N), dim3(threads), 0, stream, src, ld, positions, tok_seq, slots, inv_freq,
+                                 H, G, dk, dv, rot, (float*)q_out, (float*)cache, total_rows, status);
+    if (dtype == 1)
+        return cw_launch_ordered(rotate_store_kernel<bf16>, dim3(N), dim3(threads), 0, stream, src, ld, positions, tok_seq, slots, inv_freq,
+                                 H, G, dk, dv, rot, (bf16*)q_out, (bf16*)cache, total_rows, status);
+    return CW_ERR_BAD_DTYPE;
+}
+
 struct WindowAttentionArgs {
     const void* q;            // [N, ldq]: head h's query at columns h*dk ..
     int ldq;
@@ -67,6 +133,8 @@ struct WindowAttentionArgs {
     const float* talk;        // [H, H] or null: score_h <- sum_g talk[h, g] score_g
     const float* head_bias;   // [H] or null: added to the mixed score
     int sigmoid_weights;      // 0: softmax over the visible keys; 1: sigmoid of each score, not normalised
+    int blocked;              // 0: p sees the last `window` positions; 1: p sees its own block of `window` positions up to itself
+    const float* sink;        // [H] or null: a logit per head that counts once in the softmax's denominator
     void* out;                // [N, H*dv]
     int tile;                 // keys per tile (<= 32)
     int parts, part_keys;     // a token's window in `parts` pieces of `part_keys` keys (a multiple of tile)
@@ -91,7 +159,7 @@ window_attention_kernel(const WindowAttentionArgs a) {
         return;
     }
     const int p = a.positions[n];
-    const int first = max(0, p - a.window + 1);
+    const int first = a.blocked ? p - p % a.window : max(0, p - a.window + 1);
     const int lo = first + part * a.part_keys;
     const int hi = min(p + 1, lo + a.part_keys);  // keys lo .. hi-1
     const int GK = G * dk, kstride = GK | 1;
@@ -197,6 +265,11 @@ window_attention_kernel(const WindowAttentionArgs a) {
         }
     }
     __syncthreads();
+    if (a.sink != nullptr && partial == nullptr && !a.sigmoid_weights) {  // (cut windows: the merge adds it)
+        for (int h = tid; h < H; h += blockDim.x)
+            if (mrun[h] != -INFINITY) lrun[h] += expf(a.sink[h] - mrun[h]);
+        __syncthreads();
+    }
 #pragma unroll
     for (int r = 0; r < WA_MAX_COLS; ++r) {
         const int col = tid + r * blockDim.x;
@@ -220,7 +293,8 @@ window_attention_kernel(const WindowAttentionArgs a) {
 template <typename T>
 __global__ void __launch_bounds__(256)
 window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ positions, const int* __restrict__ tok_seq,
-                    int H, int dv, int window, int parts, int part_keys, int sigmoid_weights, int all_parts, T* __restrict__ out) {
+                    int H, int dv, int window, int parts, int part_keys, int sigmoid_weights, int all_parts, int blocked,
+                    const float* __restrict__ sink, T* __restrict__ out) {
     __shared__ float factor[64];
     __shared__ float denominator;
     pdl_wait();
@@ -228,7 +302,7 @@ window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ p
     if (tok_seq[n] < 0) return;  // (the attention kernel wrote the zeros)
     const int HV = H * dv, stride = HV + 2 * H;
     const int p = positions[n];
-    const int keys = p + 1 - max(0, p - window + 1);
+    const int keys = blocked ? p % window + 1 : p + 1 - max(0, p - window + 1);
     const int used = all_parts ? parts : (keys + part_keys - 1) / part_keys;  // (parts that hold none of the row's keys add nothing)
     const float* base = partial + (size_t)n * parts * stride;
     if (threadIdx.x == 0) {
@@ -241,6 +315,7 @@ window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ p
             factor[s] = f;
             l = fmaf(f, base[(size_t)s * stride + HV + H + h], l);
         }
+        if (sink != nullptr && !sigmoid_weights && m != -INFINITY) l += expf(sink[h] - m);
         denominator = sigmoid_weights ? 1.f : l;
     }
     __syncthreads();
@@ -346,7 +421,7 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     const int h = g0 * per + warp;  // this warp's query head
     const int gl = warp / per;      // its key/value head among the block's
     const int p0 = a.positions[row0];
-    const int first = max(0, p0 - a.window + 1);
+    const int first = a.blocked ? p0 - p0 % a.window : max(0, p0 - a.window + 1);
     // the keys that the tile's rows see, first .. p0 + rows - 1, in `parts` equal pieces of whole key tiles
     const int part_keys = a.parts > 1 ? ((p0 + rows - first + a.parts - 1) / a.parts + WM_BN - 1) / WM_BN * WM_BN : p0 + rows - first;
     const int lo = first + part * part_keys;
@@ -423,6 +498,13 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     for (int nt = 0; nt < DVMAX / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int r_lo = lane >> 2, cpair = (lane & 3) * 2;  // this thread's rows r_lo and r_lo + 8, columns cpair, cpair + 1 of a tile of 8
+    int row_first[2];  // the first position that each of the thread's two rows sees
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int p = p0 + r_lo + 8 * x;
+        row_first[x] = a.blocked ? p - p % a.window : p - a.window + 1;
+    }
+    const int last_first = a.blocked ? (p0 + 15) - (p0 + 15) % a.window : p0 + 15 - a.window + 1;  // of the tile's last row
     const float head_scale = a.head_scale != nullptr ? a.head_scale[h] : 1.f;
     const float head_bias = a.head_bias != nullptr ? a.head_bias[h] : 0.f;
     const int nvt = dv / 8, nks = dk / 16;
@@ -484,7 +566,7 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
         float tile_max[2] = {-INFINITY, -INFINITY};
         // (a tile that every row sees whole needs no mask: its last key is not behind the first row, its first not
         // before the last row's window)
-        const bool whole = rows == 16 && j0 + WM_BN - 1 <= p0 && j0 > p0 + 15 - a.window && j0 + WM_BN <= hi;
+        const bool whole = rows == 16 && j0 + WM_BN - 1 <= p0 && j0 >= last_first && j0 + WM_BN <= hi;
 #pragma unroll
         for (int nt = 0; nt < WM_BN / 8; ++nt)
 #pragma unroll
@@ -493,7 +575,7 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
                 if (!whole) {
                     const int row = r_lo + (e >> 1) * 8, j = j0 + nt * 8 + cpair + (e & 1);
                     const int p = p0 + row;
-                    on = row < rows && j <= p && j > p - a.window && j < hi;
+                    on = row < rows && j <= p && j >= row_first[e >> 1] && j < hi;
                 }
                 const float v = on ? fmaf(s[nt][e], head_scale, head_bias) : -INFINITY;
                 s[nt][e] = v;
@@ -567,6 +649,8 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     for (int x = 0; x < 2; ++x) {
         l_run[x] += __shfl_xor_sync(0xffffffffu, l_run[x], 1);
         l_run[x] += __shfl_xor_sync(0xffffffffu, l_run[x], 2);
+        if (a.sink != nullptr && a.parts == 1 && !a.sigmoid_weights && m_run[x] != -INFINITY)  // (cut rows: the merge adds it)
+            l_run[x] += __expf(a.sink[h] - m_run[x]);
     }
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
@@ -643,8 +727,9 @@ extern "C" long long cw_window_attention_partial_words(int N, int H, int dv, int
 extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, const int* block_tables, int max_blocks,
                                    int page_size, int num_pages, const int* positions, const int* tok_seq, int N, int H,
                                    int G, int dk, int dv, int window, float scale, const float* head_scale,
-                                   const float* talk, const float* head_bias, int sigmoid_weights, void* out, int parts,
-                                   float* partial, const int* q_start, int S, int dtype, int* status, cudaStream_t stream) {
+                                   const float* talk, const float* head_bias, int sigmoid_weights, int blocked, const float* sink,
+                                   void* out, int parts, float* partial, const int* q_start, int S, int dtype, int* status,
+                                   cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || window <= 0 || page_size <= 0 || max_blocks <= 0 ||
         ldq < H * dk || parts < 1)
@@ -656,14 +741,15 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     while (merge_threads < 256 && merge_threads < dv) merge_threads *= 2;
     if (dtype == 1) {  // bfloat16: the tensor-core form when it takes the sizes
         const WindowAttentionArgs base = {q, ldq, cache, block_tables, max_blocks, page_size, num_pages, positions, tok_seq, H, G, dk, dv,
-                                          window, scale, head_scale, talk, head_bias, sigmoid_weights, out, WM_BN, parts, 0, partial, status};
+                                          window, scale, head_scale, talk, head_bias, sigmoid_weights, blocked, sink, out, WM_BN, parts, 0,
+                                          partial, status};
         int launched = 0;
         const int rc = window_attention_mma(base, q_start, S, N, stream, &launched);
         if (rc != 0) return rc;
         if (launched) {
             if (parts == 1) return CW_OK;
             return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq, H,
-                                     dv, window, parts, 0, sigmoid_weights, 1, (bf16*)out);
+                                     dv, window, parts, 0, sigmoid_weights, 1, blocked, sink, (bf16*)out);
         }
     }
     int threads = 128;
@@ -680,8 +766,8 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     int part_keys = (window + parts - 1) / parts;
     part_keys = (part_keys + tile - 1) / tile * tile;
     WindowAttentionArgs a = {q, ldq, cache, block_tables, max_blocks, page_size, num_pages, positions, tok_seq, H, G, dk, dv,
-                             window, scale, head_scale, talk, head_bias, sigmoid_weights, out, tile, parts, part_keys, partial,
-                             status};
+                             window, scale, head_scale, talk, head_bias, sigmoid_weights, blocked, sink, out, tile, parts, part_keys,
+                             partial, status};
     static size_t allowed[2] = {48 << 10, 48 << 10};
     if (dtype != 0 && dtype != 1) return CW_ERR_BAD_DTYPE;
     if (smem > allowed[dtype]) {
@@ -697,9 +783,9 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     if (rc != 0 || parts == 1) return rc;
     if (dtype == 0)
         return cw_launch_ordered(window_merge_kernel<float>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq,
-                                 H, dv, window, parts, part_keys, sigmoid_weights, 0, (float*)out);
+                                 H, dv, window, parts, part_keys, sigmoid_weights, 0, blocked, sink, (float*)out);
     return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq, H,
-                             dv, window, parts, part_keys, sigmoid_weights, 0, (bf16*)out);
+                             dv, window, parts, part_keys, sigmoid_weights, 0, blocked, sink, (bf16*)out);
 }
 
 CW_TRACE_TU(window_attention)

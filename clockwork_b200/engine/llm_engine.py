@@ -71,7 +71,7 @@ class LLMEngine:
         if self.cache.groups:
             # prefixes can be shared by pages only when pages are all a request keeps: one group of layers
             # that keep every key, and no mixer with state of its own
-            pages_only = (len(self.cache.groups) == 1 and self.cache.groups[0].need.window is None
+            pages_only = (len(self.cache.groups) == 1 and self.cache.groups[0].need.window is None and self.cache.groups[0].need.block is None
                           and not self.cache.state.needs and all(isinstance(n, PagedKVNeed) for n in needs.values()))
             self.prefix_cache = PrefixCache(self.cache.groups[0].allocator, cfg.cache.block_size,
                                             enabled=cfg.cache.enable_prefix_cache and pages_only)

@@ -65,7 +65,8 @@ class TraceSession:
         self.uses_graphs = graphs and self.runner.enable_graphs(max_ctx=num_pages * page_size, max_batch=max_live)
         self.prefix: PrefixCache | None = None
         if prefix_cache:
-            if len(self.cache.groups) != 1 or self.cache.groups[0].need.window is not None or self.cache.state.needs:
+            if (len(self.cache.groups) != 1 or self.cache.groups[0].need.window is not None or self.cache.groups[0].need.block is not None
+                    or self.cache.state.needs):
                 raise ValueError("--prefix-cache needs a model whose layers all keep every key (one group of pages)")
             self.prefix = PrefixCache(self.cache.groups[0].allocator, page_size)
         self._history: dict[str, list[int]] = {}  # tokens of each live request so far (prefix cache only)

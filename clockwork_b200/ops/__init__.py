@@ -93,8 +93,8 @@ def raise_on_status(status: torch.Tensor) -> None:
         raise RuntimeError("kernel status: " + STATUS_MESSAGES.get(code, f"code {code}").format(a=a, b=b))
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: bool = False) -> torch.Tensor:
-    """float32 [N, H] rows of ``table`` (float32 or bfloat16 [V, H]) for int32 ``ids`` [N].  ``serial``: the
+def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: bool = False, scale: float = 1.0) -> torch.Tensor:
+    """float32 [N, H] rows of ``table`` (float32 or bfloat16 [V, H]) for int32 ``ids`` [N], times ``scale``.  ``serial``: the
     kernel starts only when everything before it on the stream has finished (for a step whose inputs a
     kernel has just written: the step's later kernels read them before they wait for anything)."""
     _need(table, None, "table", 2)
@@ -103,7 +103,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: 
     out = torch.empty((n, h), dtype=torch.float32, device=table.device)
 
     def launch():
-        check(library().cw_embed(_ptr(out), _ptr(table), _ptr(ids), n, h, v, dtype_code(table.dtype), _ptr(status), _stream()), "embed")
+        check(library().cw_embed(_ptr(out), _ptr(table), _ptr(ids), n, h, v, dtype_code(table.dtype), float(scale), _ptr(status), _stream()), "embed")
 
     if serial:
         with serial_launch():
@@ -140,6 +140,31 @@ def pair_rmsnorm_add(resid: torch.Tensor, a: torch.Tensor, b: torch.Tensor, wa: 
             raise ValueError(f"{name} must have {w} entries")
     check(library().cw_pair_rmsnorm_add(_ptr(resid), _ptr(a), _ptr(b), _ptr(wa), _ptr(wb), float(eps), float(factor), n, w, _stream()),
           "pair_rmsnorm_add")
+
+
+def sum_rmsnorm_add(resid: torch.Tensor, terms, weight: torch.Tensor, eps: float) -> None:
+    """``resid += rmsnorm(sum of c * t over the terms) * weight``: ``terms`` is one or two pairs (float32 [N, W], factor)."""
+    _need(resid, torch.float32, "resid", 2)
+    _need(weight, torch.float32, "weight", 1)
+    n, w = resid.shape
+    if not 1 <= len(terms) <= 2:
+        raise ValueError("one or two terms")
+    for t, _ in terms:
+        _need(t, torch.float32, "term", 2)
+        if t.shape != resid.shape:
+            raise ValueError(f"term {tuple(t.shape)} does not match the residual {tuple(resid.shape)}")
+    if weight.shape[0] != w:
+        raise ValueError(f"weight must have {w} entries")
+    (a, ca), (b, cb) = terms[0], (terms[1] if len(terms) == 2 else (None, 0.0))
+    check(library().cw_sum_rmsnorm_add(_ptr(resid), _ptr(a), _ptr(b), float(ca), float(cb), _ptr(weight), float(eps), n, w, _stream()),
+          "sum_rmsnorm_add")
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """In place on float32 ``x``: ``cap * tanh(x / cap)``."""
+    _need(x, torch.float32, "x")
+    check(library().cw_softcap(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+    return x
 
 
 class PartialSums:

@@ -29,19 +29,26 @@ def per_head_product(a: torch.Tensor, a_head_width: int, w: torch.Tensor, out: t
         _need(gate, a.dtype, "gate", 2)
     check(library().cw_grouped_gemm(_ptr(a), a.shape[1], a_head_width, _ptr(w), None, n * k, _ptr(out), out.shape[1], out_head_width,
                                     None, None, 1, None, _ptr(gate), gate.shape[1] if gate is not None else 0, rows, n, k, heads,
-                                    EPI_SIGMOID_GATE if gate is not None else EPI_STORE, dtype_code(a.dtype), _stream()),
+                                    EPI_SIGMOID_GATE if gate is not None else EPI_STORE, 0.0, dtype_code(a.dtype), _stream()),
           "per_head_product")
     return out
 
 
-def moe_choose(logits: torch.Tensor, bias: torch.Tensor | None, tok_seq: torch.Tensor, top: int):
+SCORE_CHOSEN, SCORE_ALL = 0, 1
+
+
+def moe_choose(logits: torch.Tensor, bias: torch.Tensor | None, tok_seq: torch.Tensor, top: int, scoring: int = SCORE_CHOSEN,
+               groups: int = 1, keep: int = 1):
     """(chosen experts int32 [N, top], their weights float32 [N, top]) from float32 router logits [N, E] (+ bias): the
-    ``top`` largest, weighted by the softmax over the chosen ones; padding rows choose -1."""
+    ``top`` largest, weighted by the softmax over the chosen ones (``SCORE_CHOSEN``) or by their shares of the softmax
+    over all experts, not renormalised (``SCORE_ALL``); with ``groups`` > 1 only experts of the ``keep`` best of ``groups``
+    equal runs of neighbours can be chosen (a run counts as its largest entry); padding rows choose -1."""
     _need(logits, torch.float32, "logits", 2)
     n, e = logits.shape
     sel = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    check(library().cw_moe_choose(_ptr(logits), _ptr(bias), _ptr(tok_seq), _ptr(sel), _ptr(wt), n, e, top, _stream()), "moe_choose")
+    check(library().cw_moe_choose(_ptr(logits), _ptr(bias), _ptr(tok_seq), _ptr(sel), _ptr(wt), n, e, top, int(scoring), int(groups), int(keep),
+                                  _stream()), "moe_choose")
     return sel, wt
 
 
@@ -55,14 +62,16 @@ def moe_group(sel: torch.Tensor, experts: int):
     return offsets, order
 
 
-def expert_gate_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor,
-                   top: int) -> torch.Tensor:
-    """silu(x Wg_e^T) * (x Wu_e^T) for every pair, rows in sorted order; weights [E, ff, W]."""
+def expert_gate_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, offsets: torch.Tensor | None, order: torch.Tensor | None,
+                   top: int, limit: float = 0.0) -> torch.Tensor:
+    """silu(x Wg_e^T) * (x Wu_e^T) for every pair, rows in sorted order; weights [E, ff, W].  With a positive ``limit`` the
+    clamped form ``a sigmoid(1.702 a) (b + 1)``, ``a = min(x Wg^T, limit)``, ``b = clamp(x Wu^T, -limit, limit)``.
+    ``offsets`` and ``order`` None: every row of ``x`` through every one of the E matrices (one: a dense layer)."""
     experts, ff, w = w_gate.shape
-    pairs = order.numel()
+    pairs = order.numel() if order is not None else x.shape[0]
     act = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
     check(library().cw_grouped_gemm(_ptr(x), x.shape[1], 0, _ptr(w_gate), _ptr(w_up), ff * w, _ptr(act), ff, 0, _ptr(offsets),
-                                    _ptr(order), top, None, None, 0, pairs, ff, w, experts, EPI_SILU_MUL, dtype_code(x.dtype),
+                                    _ptr(order), top, None, None, 0, pairs, ff, w, experts, EPI_SILU_MUL, float(limit), dtype_code(x.dtype),
                                     _stream()), "expert_gate_up")
     return act
 
@@ -73,7 +82,7 @@ def expert_down(act: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, 
     pairs = order.numel()
     y = torch.empty((pairs, w), dtype=torch.float32, device=act.device)
     check(library().cw_grouped_gemm(_ptr(act), ff, 0, _ptr(w_down), None, w * ff, _ptr(y), w, 0, _ptr(offsets), None, 1, _ptr(order),
-                                    None, 0, pairs, w, ff, experts, EPI_STORE_F32, dtype_code(act.dtype), _stream()), "expert_down")
+                                    None, 0, pairs, w, ff, experts, EPI_STORE_F32, 0.0, dtype_code(act.dtype), _stream()), "expert_down")
     return y
 
 

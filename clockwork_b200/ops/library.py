@@ -13,7 +13,7 @@ P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 
 # name -> argument types (the stream is the last c_void_p of each)
 _SIGNATURES: dict[str, list] = {
-    "cw_embed": [P, P, P, I, I, I, I, P, P],
+    "cw_embed": [P, P, P, I, I, I, I, F, P, P],
     "cw_add_rmsnorm": [P, P, P, P, P, I, I, I, F, I, P, P],
     "cw_silu_mul": [P, P, I, I, I, P],
     "cw_add_to_residual": [P, P, I, I, I, P],
@@ -43,17 +43,26 @@ _SIGNATURES: dict[str, list] = {
     # attention over a window of rows [key | value] (csrc/window_attention.cu); absolute positions and the sum of two normed
     # contributions (csrc/embed_norm.cu)
     "cw_store_rows": [P, I, I, I, P, P, I, LL, I, P, P],
-    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, P, I, P, P, I, I, P, P],
+    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, I, P, P, I, P, P, I, I, P, P],
+    "cw_rotate_store": [P, I, P, P, P, P, I, I, I, I, I, I, P, P, LL, I, P, P],
     "cw_window_attention_set_mma": [I],
     "cw_scale_add_sinusoid": [P, P, P, F, I, I, P],
     "cw_pair_rmsnorm_add": [P, P, P, P, P, F, F, I, I, P],
+    "cw_sum_rmsnorm_add": [P, P, P, F, F, P, F, I, I, P],
+    "cw_softcap": [P, LL, F, P],
     # products in groups and the mixture of experts (csrc/grouped_gemm.cu)
-    "cw_grouped_gemm": [P, I, I, P, P, LL, P, I, I, P, P, I, P, P, I, I, I, I, I, I, I, P],
+    "cw_grouped_gemm": [P, I, I, P, P, LL, P, I, I, P, P, I, P, P, I, I, I, I, I, I, F, I, P],
     "cw_grouped_gemm_set_mma": [I],
     "cw_latent_attention_set_mma": [I],
-    "cw_moe_choose": [P, P, P, P, P, I, I, I, P],
+    "cw_moe_choose": [P, P, P, P, P, I, I, I, I, I, I, P],
     "cw_moe_group": [P, P, P, P, I, I, P],
     "cw_moe_combine": [P, P, P, P, I, I, I, P],
+    # the delta rule, the gates and the read-out of a matrix memory (csrc/recurrence_gated.cu)
+    "cw_unit_heads": [P, I, I, I, I, F, I, F, F, P],
+    "cw_delta_coefficients": [P, I, P, P, P, I, I, I, I, P],
+    "cw_delta_scan": [P, I, P, I, P, I, P, I, P, I, P, LL, LL, P, P, P, I, I, I, I, I, P, I, P],
+    "cw_gate_scan": [P, I, P, I, P, P, F, P, LL, LL, P, P, P, I, I, P, P],
+    "cw_memory_norm": [P, P, I, P, I, P, P, I, I, I, F, I, P],
     # attention over a cached latent (csrc/latent_attention.cu)
     "cw_latent_prepare": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P, P],
     "cw_latent_attention": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],

@@ -12,7 +12,7 @@ import torch
 from . import _need, _ptr, _stream, dtype_code
 from .library import check, library
 
-FORM_CHANNEL_DECAY, FORM_STEP_SIZE, FORM_CHANNEL_DECAY_AFTER, FORM_HEAD_DECAY = 0, 1, 2, 3
+FORM_CHANNEL_DECAY, FORM_STEP_SIZE, FORM_CHANNEL_DECAY_AFTER, FORM_HEAD_DECAY, FORM_GATED_WITH_KEY_SUM = 0, 1, 2, 3, 4
 ACT_GELU_TANH, ACT_TANH, ACT_SILU, ACT_SIGMOID = 0, 1, 2, 3
 GATE_SILU, GATE_SIGMOID = 0, 1
 
@@ -97,6 +97,84 @@ def recurrence_scan(form: int, q, k, v, pre, p0, p1, p2, view, offset: int, ctx,
                                        _ptr(p0), _ptr(p1), _ptr(p2), state, stride, offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start),
                                        ctx.num_seqs, heads, dk, dv, heads_per_group, _ptr(out), heads * dv, float(q_scale), _stream()),
           "recurrence_scan")
+    return out
+
+
+def unit_heads_(x: torch.Tensor, heads: int, dim: int, eps: float, leading: int, leading_scale: float, scale: float = 1.0) -> torch.Tensor:
+    """In place on the first ``heads*dim`` columns of float32 ``x`` [N, C]: every head divided by ``sqrt(sum of squares + eps)``,
+    the first ``leading`` heads then times ``leading_scale``, the others times ``scale``."""
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1 or x.shape[1] < heads * dim:
+        raise ValueError("x must be float32 [N, >= heads*dim] with unit column stride")
+    n = x.shape[0]
+    check(library().cw_unit_heads(_ptr(x), x.stride(0) if n > 1 else max(x.stride(0), x.shape[1]), n, heads, dim, float(eps), int(leading),
+                                  float(leading_scale), float(scale), _stream()), "unit_heads")
+    return x
+
+
+def delta_scan(q, k, v, pre, beta, dt_bias, a_log, view, offset: int, ctx, heads: int, dk: int, dv: int,
+               heads_per_group: int = 1) -> torch.Tensor:
+    """float32 [N, heads*dv]: the gated delta rule ``S <- diag(a) S; u = beta (v - S^T k); S <- S + k u^T; y = S^T q`` per
+    head, with ``a = exp(-exp(a_log[h]) softplus(pre + dt_bias))`` and ``beta = sigmoid(beta)``, both made in place from the
+    products' outputs (nothing else reads them).  ``q``, ``k`` [N, groups*dk], ``v`` [N, heads*dv], ``pre`` [N, heads*dk],
+    ``beta`` [N, heads]: float32, unit column stride, any row stride.  The state piece at ``offset`` holds heads*dk*dv numbers."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("pre", pre), ("beta", beta)):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be float32 [N, *] with unit column stride")
+    _need(dt_bias, torch.float32, "dt_bias", 1)
+    _need(a_log, torch.float32, "a_log", 1)
+    if dt_bias.shape[0] != heads * dk or a_log.shape[0] != heads:
+        raise ValueError("dt_bias must have heads*dk entries and a_log heads")
+    n = v.shape[0]
+    out = torch.empty((n, heads * dv), dtype=torch.float32, device=v.device)
+    state, stride, slots = _state_args(view)
+
+    def ld(t):
+        return t.stride(0) if n > 1 else max(t.stride(0), t.shape[1])
+
+    check(library().cw_delta_coefficients(_ptr(pre), ld(pre), _ptr(dt_bias), _ptr(a_log), _ptr(beta), ld(beta), n, heads, dk, _stream()),
+          "delta_coefficients")
+    check(library().cw_delta_scan(_ptr(q), ld(q), _ptr(k), ld(k), _ptr(v), ld(v), _ptr(pre), ld(pre), _ptr(beta), ld(beta), state, stride,
+                                  offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start), ctx.num_seqs, heads, dk, dv, heads_per_group,
+                                  _ptr(out), heads * dv, _stream()), "delta_scan")
+    return out
+
+
+def gate_scan(zi: torch.Tensor, zf: torch.Tensor, bias_i: torch.Tensor | None, bias_f: torch.Tensor | None, cap: float, view,
+              offset: int, ctx, heads: int) -> torch.Tensor:
+    """float32 [N, 3*heads] = ``[keep | take | floor]`` per token and head from the pre-activations of an input gate and a
+    forget gate (``zi``, ``zf`` [N, heads], float32, any row stride): ``li = cap tanh((zi + bias_i)/cap)``,
+    ``lf = log sigmoid(cap tanh((zf + bias_f)/cap))``, ``m_t = max(lf + m_(t-1), li)``, ``keep = exp(lf + m_(t-1) - m_t)``,
+    ``take = exp(li - m_t)``, ``floor = exp(-m_t)``.  The running maximum of every head is one float of the request's state
+    at ``offset`` (0 when a request starts)."""
+    for name, t in (("zi", zi), ("zf", zf)):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] != heads:
+            raise ValueError(f"{name} must be float32 [N, heads] with unit column stride")
+    n = zi.shape[0]
+    coef = torch.empty((n, 3 * heads), dtype=torch.float32, device=zi.device)
+    state, stride, slots = _state_args(view)
+    check(library().cw_gate_scan(_ptr(zi), zi.stride(0) if n > 1 else max(zi.stride(0), heads), _ptr(zf),
+                                 zf.stride(0) if n > 1 else max(zf.stride(0), heads), _ptr(bias_i), _ptr(bias_f), float(cap), state, stride,
+                                 offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start), ctx.num_seqs, heads, _ptr(coef), _stream()), "gate_scan")
+    return coef
+
+
+def memory_norm(y: torch.Tensor, floor: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, heads: int, dv: int, eps: float,
+                out_dtype: torch.dtype) -> torch.Tensor:
+    """[N, heads*dv]: ``y`` [N, heads*(dv+1)] holds per head ``[S^T q | n . q]``; every head's first dv entries are divided
+    by ``max(|n . q|, floor) + 1e-6``, then by their root mean square, times ``weight`` [heads*dv], times ``sigmoid(z)``.
+    ``floor`` [N, heads] and ``z`` [N, heads*dv]: float32, any row stride."""
+    _need(y, torch.float32, "y", 2)
+    _need(weight, torch.float32, "weight", 1)
+    for name, t in (("floor", floor), ("z", z)):
+        if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{name} must be float32 [N, *] with unit column stride")
+    n = y.shape[0]
+    if y.shape[1] != heads * (dv + 1) or weight.shape[0] != heads * dv:
+        raise ValueError("y must be [N, heads*(dv+1)] and weight [heads*dv]")
+    out = torch.empty((n, heads * dv), dtype=out_dtype, device=y.device)
+    check(library().cw_memory_norm(_ptr(y), _ptr(floor), floor.stride(0) if n > 1 else max(floor.stride(0), heads), _ptr(z),
+                                   z.stride(0) if n > 1 else max(z.stride(0), heads * dv), _ptr(weight), _ptr(out), n, heads, dv, float(eps),
+                                   dtype_code(out_dtype), _stream()), "memory_norm")
     return out
 
 

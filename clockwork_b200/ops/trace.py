@@ -19,7 +19,7 @@ import torch
 from .library import check, library
 
 _TUS = ("attention_decode", "attention_decode_large", "attention_decode_mid", "attention_prefill", "attention_prefill_tc", "attention_ref", "embed_norm", "gemm_ref",
-        "gemm_tc", "grouped_gemm", "latent_attention", "recurrence", "rope_cache", "sampling")
+        "gemm_tc", "grouped_gemm", "latent_attention", "recurrence", "recurrence_gated", "rope_cache", "sampling", "window_attention")
 _WORDS = 8
 _buf: torch.Tensor | None = None
 

@@ -46,6 +46,30 @@ def store_rows(src: torch.Tensor, col0: int, width: int, cache_rows: torch.Tenso
                                   _ptr(slots), n, total, dtype_code(src.dtype), _ptr(status), _stream()), "store_rows")
 
 
+def rotate_store(src: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, slots: torch.Tensor | None, inv_freq: torch.Tensor | None,
+                 heads: int, kv_heads: int, dk: int, dv: int, rot: int, cache_rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """From the float32 product rows ``src`` [N, >= heads*dk + kv_heads*(dk + dv)] (queries, then ``[key | value]`` per
+    key/value head): the first ``rot`` entries of every query and key head turned by the token's position (entry i with
+    entry i + rot/2 by ``position * inv_freq[i]``, float32 angles); returns the queries [N, heads*dk] in the cache's dtype
+    and stores the rows ``[key | value]`` where ``slots`` says (None: nothing is stored)."""
+    if src.dtype != torch.float32 or src.dim() != 2 or src.stride(1) != 1:
+        raise ValueError("src must be float32 [N, C] with unit column stride")
+    _need(cache_rows, None, "cache", 4)
+    if tuple(cache_rows.shape[2:]) != (kv_heads, dk + dv):
+        raise ValueError(f"cache rows {tuple(cache_rows.shape)} are not [pages, page_size, {kv_heads}, {dk + dv}]")
+    if rot:
+        _need(inv_freq, torch.float32, "inv_freq", 1)
+        if inv_freq.shape[0] * 2 != rot:
+            raise ValueError(f"inv_freq has {inv_freq.shape[0]} entries for {rot} rotated dimensions")
+    n = src.shape[0]
+    q = torch.empty((n, heads * dk), dtype=cache_rows.dtype, device=src.device)
+    total = cache_rows.shape[0] * cache_rows.shape[1]
+    check(library().cw_rotate_store(_ptr(src), src.stride(0) if n > 1 else max(src.stride(0), src.shape[1]), _ptr(positions), _ptr(tok_seq),
+                                    _ptr(slots), _ptr(inv_freq) if rot else None, n, heads, kv_heads, dk, dv, rot, _ptr(q), _ptr(cache_rows),
+                                    total, dtype_code(cache_rows.dtype), _ptr(status), _stream()), "rotate_store")
+    return q
+
+
 def window_parts(num_tokens: int, window: int, dtype: torch.dtype) -> int:
     """In how many pieces the keys of a row are cut (the pieces are added up by a second kernel).  float32 runs never
     cut: their results do not depend on the step's size to the last bit.  bfloat16: finely when a step has so few
@@ -66,9 +90,12 @@ def reserve_window_scratch(device, heads: int, dv: int) -> None:
 def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: torch.Tensor, positions: torch.Tensor,
                      tok_seq: torch.Tensor, q_start: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, window: int, scale: float,
                      head_scale: torch.Tensor | None, talk: torch.Tensor | None, head_bias: torch.Tensor | None,
-                     sigmoid_weights: bool, status: torch.Tensor, parts: int = 1) -> torch.Tensor:
+                     sigmoid_weights: bool, status: torch.Tensor, parts: int = 1, blocked: bool = False,
+                     sink: torch.Tensor | None = None) -> torch.Tensor:
     """[N, heads*dv] in ``q``'s dtype.  ``q`` [N, >= heads*dk] (queries in the leading columns, unit column stride);
-    ``cache_rows`` [pages, page_size, kv_heads, dk + dv]; the step's tokens are already stored there."""
+    ``cache_rows`` [pages, page_size, kv_heads, dk + dv]; the step's tokens are already stored there.  ``blocked``:
+    positions are cut into blocks of ``window`` and a token sees its own block up to itself, instead of the last
+    ``window`` positions.  ``sink`` [heads]: a logit per head that enters the softmax's denominator once."""
     if q.dim() != 2 or q.stride(1) != 1 or q.shape[1] < heads * dk:
         raise ValueError("q must be [N, >= heads*dk] with unit column stride")
     _need(cache_rows, q.dtype, "cache", 4)
@@ -76,7 +103,10 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
         raise ValueError(f"cache rows {tuple(cache_rows.shape)} are not [pages, page_size, {kv_heads}, {dk + dv}]")
     _need(block_tables, torch.int32, "block_tables", 2)
     _need(q_start, torch.int32, "q_start", 1)
-    for name, t, size in (("head_scale", head_scale, heads), ("talk", talk, heads * heads), ("head_bias", head_bias, heads)):
+    if sink is not None and sigmoid_weights:
+        raise ValueError("a sink belongs to softmax weights")
+    for name, t, size in (("head_scale", head_scale, heads), ("talk", talk, heads * heads), ("head_bias", head_bias, heads),
+                          ("sink", sink, heads)):
         if t is not None:
             _need(t, torch.float32, name)
             if t.numel() != size:
@@ -91,6 +121,7 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
     check(library().cw_window_attention(
         _ptr(q), q.stride(0) if n > 1 else max(q.stride(0), q.shape[1]), _ptr(cache_rows), _ptr(block_tables), block_tables.shape[1],
         cache_rows.shape[1], cache_rows.shape[0], _ptr(positions), _ptr(tok_seq), n, heads, kv_heads, dk, dv, int(window), float(scale),
-        _ptr(head_scale), _ptr(talk), _ptr(head_bias), 1 if sigmoid_weights else 0, _ptr(out), parts, _ptr(partial),
+        _ptr(head_scale), _ptr(talk), _ptr(head_bias), 1 if sigmoid_weights else 0, 1 if blocked else 0, _ptr(sink), _ptr(out), parts,
+        _ptr(partial),
         _ptr(q_start), q_start.shape[0] - 1, dtype_code(q.dtype), _ptr(status), _stream()), "window_attention")
     return out

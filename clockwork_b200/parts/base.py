@@ -35,7 +35,9 @@ Fetch = Callable[[str], torch.Tensor]
 @dataclass(frozen=True)
 class PagedKVNeed:
     """The mixer keeps keys and values per token, in pages.  ``window``: only the last
-    ``window`` tokens are ever read (pages behind it can be given back); None: all.  ``planes``: 2 for
+    ``window`` tokens are ever read (pages behind it can be given back); None: all.  ``block``: positions are cut
+    into blocks of ``block`` and a token reads its own block only (pages of earlier blocks can be given back).
+    ``planes``: 2 for
     keys and values; 1 for a mixer that keeps one row per token (a latent that keys and values are both
     made from): its view's ``k_cache`` and ``v_cache`` are then the same tensor."""
 
@@ -43,6 +45,7 @@ class PagedKVNeed:
     head_dim: int
     window: int | None = None
     planes: int = 2
+    block: int | None = None
 
 
 @dataclass(frozen=True)
@@ -230,12 +233,23 @@ class Mixer(Part):
         (``side_by_side``) asks of each.  Optional: a mixer that only ever stands alone need not have it."""
         raise NotImplementedError(f"{type(self).__name__} cannot be used inside another mixer")
 
+    def mix_terms(self, ctx: StepContext, x: torch.Tensor, view) -> list:
+        """The mixer's output as a weighted sum that is not yet formed: one or two pairs (float32 [N, hidden], factor).
+        What a block asks for that norms the output before it adds it (``sandwich_residual``): the sum is then formed
+        inside the norm's kernel."""
+        return [(self.mix(ctx, x, view), 1.0)]
+
     def forward(self, ctx: StepContext, x: torch.Tensor, view, stream: ResidualStream) -> torch.Tensor | None:
         raise NotImplementedError
 
 
 class FeedForward(Part):
     takes_half_normed = False
+
+    def output_terms(self, ctx: StepContext, x: torch.Tensor) -> list:
+        """The feed-forward's output as one or two pairs (float32 [N, hidden], factor), added to nothing (see
+        ``Mixer.mix_terms``).  Optional: only blocks that norm the output ask for it."""
+        raise NotImplementedError(f"{type(self).__name__} cannot stand in a block that norms its output")
 
     def forward(self, ctx: StepContext, x: torch.Tensor, stream: ResidualStream) -> torch.Tensor | None:
         raise NotImplementedError

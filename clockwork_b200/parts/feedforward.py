@@ -9,7 +9,20 @@ accumulation and stay float32; each token takes
 the ``top`` experts with the largest logits, weighted by the softmax over the chosen logits only; the
 output is the weighted sum of the chosen experts' outputs, added into the float32 residual in the order
 of the choices.  Tokens are grouped by expert on the device (no host round trip), so the part is safe
-to capture in a CUDA graph.  Parameters: ``hidden_size, expert_size, experts, top``.
+to capture in a CUDA graph.  Parameters: ``hidden_size, expert_size, experts, top``, and optionally
+
+* ``scoring``: ``"chosen"`` (the default, as above) or ``"all"``: the weights are the chosen experts' shares of the
+  softmax over all experts, not renormalised;
+* ``groups, keep``: the experts lie in ``groups`` equal runs of neighbours, a run counts as its best expert, and only
+  experts of the ``keep`` best runs can be chosen;
+* ``limit``: a positive number selects the clamped activation ``a sigmoid(1.702 a) (b + 1)`` with ``a = min(gate(x),
+  limit)`` and ``b = clamp(up(x), -limit, limit)`` instead of ``silu(gate(x)) up(x)``;
+* ``router_bias``: whether the router has a bias (tensor ``router.b``; the default) or not;
+* ``shared``: ``{"size", "limit"}``: one more expert of the same form (tensors ``shared.gate|up|down``) that every token
+  uses with weight one.
+
+In a block that norms the feed-forward's output (``output_terms``) the sum of the experts' outputs is formed in a float32
+buffer of its own instead of in the residual.
 """
 
 from __future__ import annotations
@@ -61,7 +74,22 @@ class MixtureOfExperts(FeedForward):
         self.top = int(spec["top"])
         if not 0 < self.top <= self.experts:
             raise ValueError(f"top {self.top} must lie in 1..experts ({self.experts})")
+        scoring = str(spec.get("scoring", "chosen"))
+        if scoring not in ("chosen", "all"):
+            raise ValueError(f"scoring must be 'chosen' or 'all', got {scoring!r}")
+        self.scoring = grouped_ops.SCORE_ALL if scoring == "all" else grouped_ops.SCORE_CHOSEN
+        self.groups, self.keep = int(spec.get("groups", 1)), int(spec.get("keep", 1))
+        if self.groups < 1 or self.experts % self.groups or not 1 <= self.keep <= self.groups:
+            raise ValueError(f"{self.experts} experts do not lie in {self.groups} equal groups of which {self.keep} are kept")
+        if self.keep * (self.experts // self.groups) < self.top:
+            raise ValueError(f"the {self.keep} kept groups hold fewer than top = {self.top} experts")
+        self.limit = float(spec.get("limit") or 0.0)
+        self.has_router_bias = bool(spec.get("router_bias", True))
+        shared = spec.get("shared")
+        self.shared_size = int(shared["size"]) if shared else 0
+        self.shared_limit = float(shared.get("limit") or 0.0) if shared else 0.0
         self.w_gate = self.w_up = self.w_down = self.router = self.router_bias = None
+        self.shared_gate = self.shared_up = self.shared_down = None
 
     def tensor_decls(self):
         h, f = self.hidden_size, self.expert_size
@@ -70,21 +98,49 @@ class MixtureOfExperts(FeedForward):
             yield TensorDecl(self.name(f"e{e}.up"), (f, h), "matrix", "linear")
             yield TensorDecl(self.name(f"e{e}.down"), (h, f), "matrix", "linear")
         yield TensorDecl(self.name("router"), (self.experts, h), "matrix", "linear")
-        yield TensorDecl(self.name("router.b"), (self.experts,), "vector", "bias")
+        if self.has_router_bias:
+            yield TensorDecl(self.name("router.b"), (self.experts,), "vector", "bias")
+        if self.shared_size:
+            yield TensorDecl(self.name("shared.gate"), (self.shared_size, h), "matrix", "linear")
+            yield TensorDecl(self.name("shared.up"), (self.shared_size, h), "matrix", "linear")
+            yield TensorDecl(self.name("shared.down"), (h, self.shared_size), "matrix", "linear")
 
     def load_weights(self, fetch) -> None:
         stack = lambda what: torch.stack([fetch(self.name(f"e{e}.{what}")) for e in range(self.experts)]).contiguous()  # noqa: E731
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
         self.router = Linear(fetch(self.name("router")))
-        self.router_bias = fetch(self.name("router.b"))
+        self.router_bias = fetch(self.name("router.b")) if self.has_router_bias else None
+        if self.shared_size:
+            self.shared_gate = fetch(self.name("shared.gate")).unsqueeze(0).contiguous()  # one "expert" that every row goes through
+            self.shared_up = fetch(self.name("shared.up")).unsqueeze(0).contiguous()
+            self.shared_down = Linear(fetch(self.name("shared.down")))
+
+    def _routed(self, ctx: StepContext, x):
+        """(the chosen experts' outputs float32 [N*top, hidden] in choice order, the choices, their weights)."""
+        sel, weights = grouped_ops.moe_choose(self.router.to_float32(x), self.router_bias, ctx.tok_seq, self.top, self.scoring,
+                                              self.groups, self.keep)
+        offsets, order = grouped_ops.moe_group(sel, self.experts)
+        act = grouped_ops.expert_gate_up(x, self.w_gate, self.w_up, offsets, order, self.top, self.limit)
+        return grouped_ops.expert_down(act, self.w_down, offsets, order), sel, weights
+
+    def _shared_act(self, x):
+        return grouped_ops.expert_gate_up(x, self.shared_gate, self.shared_up, None, None, 1, self.shared_limit)
 
     def forward(self, ctx: StepContext, x, stream: ResidualStream):
-        sel, weights = grouped_ops.moe_choose(self.router.to_float32(x), self.router_bias, ctx.tok_seq, self.top)
-        offsets, order = grouped_ops.moe_group(sel, self.experts)
-        act = grouped_ops.expert_gate_up(x, self.w_gate, self.w_up, offsets, order, self.top)
-        y = grouped_ops.expert_down(act, self.w_down, offsets, order)
+        y, sel, weights = self._routed(ctx, x)
+        if self.shared_size:
+            self.shared_down.add_into(self._shared_act(x), stream.residual_after_flush(), None)
         grouped_ops.moe_combine(stream.residual_after_flush(), y, sel, weights)
         return None
+
+    def output_terms(self, ctx: StepContext, x):
+        y, sel, weights = self._routed(ctx, x)
+        if self.shared_size:
+            out = self.shared_down.to_float32(self._shared_act(x))
+        else:
+            out = torch.zeros((x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
+        grouped_ops.moe_combine(out, y, sel, weights)  # (the rows of no request keep what the shared expert made of them)
+        return [(out, 1.0)]
 
 
 register_ffn("gelu_mlp", GeluMLP, replace=True)

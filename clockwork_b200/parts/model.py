@@ -32,8 +32,6 @@ class DecoderModel:
         self.absolute_positions = None
         if spec.absolute_positions is not None:
             self.absolute_positions = build_part("position", spec.absolute_positions, "", dtype, self.device)
-        elif spec.embedding_scale != 1.0:
-            raise ValueError("an embedding scale needs a position part that applies it (absolute_positions)")
         self.embedding: torch.Tensor | None = None
         self.head: Linear | None = None
 
@@ -141,7 +139,9 @@ class DecoderModel:
         wanted).  Returns float32 [R, vocab], or None when no row is wanted."""
         # (kernels of a step read its inputs before they wait for their predecessors; when a kernel has
         # only just written those inputs, the first kernel here must not start before it has finished)
-        stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status, serial=ctx.inputs_from_device))
+        # (a position part multiplies the rows by the embedding's scale itself; without one the gather does)
+        scale = 1.0 if self.absolute_positions is not None else self.spec.embedding_scale
+        stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status, serial=ctx.inputs_from_device, scale=scale))
         if self.absolute_positions is not None:
             self.absolute_positions.add_to_embedding(stream.residual, ctx.positions, self.spec.embedding_scale)
         schedule = self.spec.schedule
@@ -161,7 +161,10 @@ class DecoderModel:
             stream.flush()
             return None
         x = self.final_norm.forward_rows(stream, logit_rows, ctx.status)
-        return self.head.to_float32(x)
+        logits = self.head.to_float32(x)
+        if self.spec.logit_softcap is not None:
+            ops.softcap_(logits, self.spec.logit_softcap)
+        return logits
 
 
 def tensor_decls_for_spec(spec: ModelSpec) -> list[TensorDecl]:

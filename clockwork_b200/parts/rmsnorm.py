@@ -55,6 +55,11 @@ class RMSNorm(Norm):
         delta, stream.pending = stream.pending, None
         return ops.add_rmsnorm(stream.residual, delta, self.weight, self.eps, self.dtype, status)
 
+    def add_normed(self, stream: ResidualStream, terms) -> None:
+        """``residual += norm(sum of factor * tensor over the terms) * weight``: this norm behind a sublayer, whose output
+        comes as one or two pairs (float32 [N, size], factor).  Statistics, sum and residual are float32."""
+        ops.sum_rmsnorm_add(stream.residual_after_flush(), terms, self.weight, self.eps)
+
     def forward_rows(self, stream: ResidualStream, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         stream.flush()
         return ops.rmsnorm_rows(stream.residual, rows, self.weight, self.eps, self.dtype, status)

@@ -3,9 +3,12 @@ with a weight of its own, and the mixer's result is ``factor`` times their sum:
 
     out = factor * (n(left(h)) g_left + n(right(h)) g_right),   n(y) = y / sqrt(mean(y^2) + eps)
 
+or, with ``normed = False``, the plain weighted sum ``left_scale * left(h) + right_scale * right(h)`` (no tensors of
+its own; such a mixer stands in a block that norms the sum, and hands it over as two terms: ``mix_terms``).
+
 Parameters: ``hidden_size, eps, factor`` (0.5: half the sum), ``left`` and ``right`` (the ``PartSpec`` of any
-registered mixer that has ``mix``).  Tensors: the mixers' own under ``<prefix>.left`` and ``<prefix>.right``, and the
-two weights ``left.out`` and ``right.out`` [hidden].  What the two keep per request is asked for as a tuple (pages
+registered mixer that has ``mix``); or ``normed = False, left_scale, right_scale``.  Tensors: the mixers' own under
+``<prefix>.left`` and ``<prefix>.right``, and (normed) the two weights ``left.out`` and ``right.out`` [hidden].  What the two keep per request is asked for as a tuple (pages
 of the one, a state slot of the other); the norms and the sum into the residual are one float32 kernel.
 
 The two mixers share nothing but their input, so the left one's kernels are launched on a second stream of the device
@@ -43,8 +46,10 @@ class SideBySide(Mixer):
         super().__init__(spec, prefix, dtype, device)
         p = spec.params
         self.hidden_size = int(p["hidden_size"])
-        self.eps = float(p["eps"])
+        self.normed = bool(p.get("normed", True))
+        self.eps = float(p.get("eps", 0.0))
         self.factor = float(p.get("factor", 0.5))
+        self.left_scale, self.right_scale = float(p.get("left_scale", 1.0)), float(p.get("right_scale", 1.0))
         self.left = build_part("mixer", p["left"], self.name("left"), dtype, device)
         self.right = build_part("mixer", p["right"], self.name("right"), dtype, device)
         self.graph_safe = bool(self.left.graph_safe and self.right.graph_safe)
@@ -82,16 +87,34 @@ class SideBySide(Mixer):
     def tensor_decls(self):
         yield from self.left.tensor_decls()
         yield from self.right.tensor_decls()
+        if not self.normed:
+            return
         yield TensorDecl(self.name("left.out"), (self.hidden_size,), "vector", "norm")
         yield TensorDecl(self.name("right.out"), (self.hidden_size,), "vector", "norm")
 
     def load_weights(self, fetch) -> None:
         self.left.load_weights(fetch)
         self.right.load_weights(fetch)
+        if not self.normed:
+            return
         self.left_weight = fetch(self.name("left.out")).contiguous()
         self.right_weight = fetch(self.name("right.out")).contiguous()
 
+    def mix_terms(self, ctx: StepContext, x, view):
+        if self.normed:
+            raise NotImplementedError("a side_by_side mixer that norms its two outputs adds them into the residual itself")
+        a, b = self._both(ctx, x, view)
+        return [(a, self.left_scale), (b, self.right_scale)]
+
     def forward(self, ctx: StepContext, x, view, stream: ResidualStream):
+        if not self.normed:
+            raise NotImplementedError("a side_by_side mixer without norms of its own stands in a block that norms its output")
+        a, b = self._both(ctx, x, view)
+        ops.pair_rmsnorm_add(stream.residual_after_flush(), a, b, self.left_weight, self.right_weight, self.eps, self.factor)
+        return None
+
+    def _both(self, ctx: StepContext, x, view):
+        """The two mixers' outputs (float32 [N, hidden] each), the left one's kernels on the second stream."""
         left_view, right_view = self._views(view)
         if self.concurrent and x.is_cuda:
             if self._forked is None:
@@ -107,8 +130,7 @@ class SideBySide(Mixer):
         else:
             a = self.left.mix(ctx, x, left_view)
             b = self.right.mix(ctx, x, right_view)
-        ops.pair_rmsnorm_add(stream.residual_after_flush(), a, b, self.left_weight, self.right_weight, self.eps, self.factor)
-        return None
+        return a, b
 
 
 register_mixer("side_by_side", SideBySide, replace=True)

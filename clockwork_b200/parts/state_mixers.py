@@ -29,6 +29,23 @@ vdim, decay`` (a number per head), ``eps``.  ``q, k, v = silu(W_q x), silu(W_k x
 ``S <- decay_h S + k v^T``, ``o = S^T q``.  The heads' outputs together are divided by their root mean square, times
 ``norm``, times ``sigmoid(W_g x)``, and go through ``o``.  The state slot holds S.
 
+``channel_delta`` (gated delta rule with a decay per key channel).  Parameters: ``hidden_size, heads, kv_heads, dim, vdim,
+conv, eps``; the inner sizes of the decay's and the gate's two products are whatever the checkpoint's ``a1`` and ``g1``
+have.  ``q, k`` (kv_heads x dim) and ``v`` (heads x vdim) are products of the input that pass a causal per-channel
+convolution of ``conv`` taps (tensors ``q.conv, k.conv, v.conv`` [channels, taps], the current token's tap last, no bias)
+and SiLU; q and k are then divided per head by ``sqrt(sum of squares + 1e-6)``, q also by ``sqrt(dim)``; head h reads
+q/k head ``h // (heads / kv_heads)``.  ``beta = sigmoid(W_b x)`` per head, ``a = exp(-exp(A_log[h]) softplus(W_a2 W_a1 x +
+dt_bias))`` per head and key channel.  Per head ``S <- diag(a) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q``.  Each
+head's o is divided by its root mean square, times ``norm`` (vdim entries, shared), times ``sigmoid(W_g2 W_g1 x)``, and goes
+through ``o``.  The state slot holds S of every head and the last conv-1 inputs of the convolution.
+
+``matrix_memory`` (a matrix memory with exponential gates kept stable by a running maximum).  Parameters: ``hidden_size,
+heads, dim, vdim, gate_cap, eps``.  ``q = W_q x / sqrt(dim)``, ``k, v`` plain products; per head ``li = cap tanh((W_i x +
+b_i)/cap)``, ``lf = log sigmoid(cap tanh((W_f x + b_f)/cap))``, ``m_t = max(lf + m_(t-1), li)`` (m is 0 before the first
+token), ``S <- exp(lf + m_(t-1) - m_t) S + exp(li - m_t) k v^T`` and the same for ``n`` with k alone, ``o = S^T q /
+(max(|n . q|, exp(-m_t)) + 1e-6)``.  Each head's o is divided by its root mean square, times ``norm`` (all heads' width),
+times ``sigmoid(W_g x)``, and goes through ``o``.  The state slot holds S with n as one more value column, and m.
+
 All run the recurrence itself, the decays, step sizes and norms in float32 in either run precision;
 the products that feed them write float32.  ``mix`` returns the output product as float32 for a mixer that
 stands beside another (``side_by_side``).
@@ -255,6 +272,132 @@ class DecayLinearMixer(_LinearAttention):
         return rec_ops.gated_group_norm(o, g, self.norm_w, 1, self.eps, False, self.dtype, gate=rec_ops.GATE_SIGMOID)
 
 
+class ChannelDeltaMixer(Mixer):
+    graph_safe = True
+    graph_safe_portions = True
+    UNIT_EPS = 1e-6  # inside the root of the unit vectors' lengths
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.kv_heads = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim, self.taps = int(p["dim"]), int(p["vdim"]), int(p["conv"])
+        self.eps = float(p["eps"])
+        self.decay_rank, self.gate_rank = int(p.get("decay_rank") or 16), int(p.get("gate_rank") or 16)
+        if min(self.heads, self.kv_heads, self.dim, self.vdim, self.taps) <= 0 or self.heads % self.kv_heads:
+            raise ValueError(f"heads {self.heads} must be a positive multiple of kv_heads {self.kv_heads}; dim, vdim, conv positive")
+        self.qk, self.inner = self.kv_heads * self.dim, self.heads * self.vdim
+        self.channels = 2 * self.qk + self.inner       # what passes the convolution: q, k, v
+        self.decays = self.heads * self.dim
+        self.scan_offset = 0
+        self.conv_offset = self.heads * self.dim * self.vdim
+
+    def cache_need(self) -> SlotStateNeed:
+        return SlotStateNeed((self.conv_offset + (self.taps - 1) * self.channels,))
+
+    def tensor_decls(self):
+        h = self.hidden_size
+        for s, out in (("q", self.qk), ("k", self.qk), ("v", self.inner)):
+            yield TensorDecl(self.name(s), (out, h), "matrix", "linear")
+            yield TensorDecl(self.name(f"{s}.conv"), (out, self.taps), "vector", "norm")
+        yield TensorDecl(self.name("b"), (self.heads, h), "matrix", "linear")
+        yield TensorDecl(self.name("A_log"), (self.heads,), "vector", "bias")
+        yield TensorDecl(self.name("norm"), (self.vdim,), "vector", "norm")
+        yield TensorDecl(self.name("a1"), (self.decay_rank, h), "matrix", "linear", free_dims=(0,))
+        yield TensorDecl(self.name("a2"), (self.decays, self.decay_rank), "matrix", "linear", free_dims=(1,))
+        yield TensorDecl(self.name("dt_bias"), (self.decays,), "vector", "bias")
+        yield TensorDecl(self.name("g1"), (self.gate_rank, h), "matrix", "linear", free_dims=(0,))
+        yield TensorDecl(self.name("g2"), (self.inner, self.gate_rank), "matrix", "linear", free_dims=(1,))
+        yield TensorDecl(self.name("o"), (h, self.inner), "matrix", "linear")
+
+    def load_weights(self, fetch) -> None:
+        self.w_in = Linear(torch.cat([fetch(self.name(s)) for s in ("q", "k", "v", "b")], dim=0).contiguous())
+        self.conv_w = torch.cat([fetch(self.name(f"{s}.conv")) for s in ("q", "k", "v")], dim=0).contiguous()
+        self.a_log, self.dt_bias = fetch(self.name("A_log")).contiguous(), fetch(self.name("dt_bias")).contiguous()
+        self.norm_w = fetch(self.name("norm")).contiguous()
+        self.a1, self.a2 = Linear(fetch(self.name("a1"))), Linear(fetch(self.name("a2")))
+        self.g1, self.g2 = Linear(fetch(self.name("g1"))), Linear(fetch(self.name("g2")))
+        for first, second in ((self.a1, self.a2), (self.g1, self.g2)):
+            if first.out_features != second.in_features:
+                raise ValueError(f"{self.prefix}: a product of {first.out_features} rows feeds one of {second.in_features} columns")
+        self.o = Linear(fetch(self.name("o")))
+
+    def _gated_output(self, ctx: StepContext, x, view: StateView):
+        qk, c = self.qk, self.channels
+        proj = self.w_in.to_float32(x)  # [N, q | k | v | beta], float32
+        raw = proj[:, :c]
+        qkv = rec_ops.causal_conv(raw, self.conv_w, None, view, self.conv_offset, ctx)
+        rec_ops.carry_rows(raw, self.taps - 1, view, self.conv_offset, ctx)  # after the convolution has read the old rows
+        rec_ops.unit_heads_(qkv, 2 * self.kv_heads, self.dim, self.UNIT_EPS, self.kv_heads, self.dim ** -0.5)
+        pre = self.a2.to_float32(self.a1(x))
+        o = rec_ops.delta_scan(q=qkv[:, :qk], k=qkv[:, qk : 2 * qk], v=qkv[:, 2 * qk :], pre=pre, beta=proj[:, c:],
+                               dt_bias=self.dt_bias, a_log=self.a_log, view=view, offset=self.scan_offset, ctx=ctx, heads=self.heads,
+                               dk=self.dim, dv=self.vdim, heads_per_group=self.heads // self.kv_heads)
+        gate = self.g2.to_float32(self.g1(x))
+        return rec_ops.gated_group_norm(o, gate, self.norm_w, self.heads, self.eps, False, self.dtype, gate=rec_ops.GATE_SIGMOID,
+                                        shared_weight=True)
+
+    def mix(self, ctx: StepContext, x, view: StateView):
+        return self.o.to_float32(self._gated_output(ctx, x, view))
+
+    def forward(self, ctx: StepContext, x, view: StateView, stream: ResidualStream):
+        return self.o.add_or_defer(self._gated_output(ctx, x, view), stream)
+
+
+class MatrixMemoryMixer(Mixer):
+    graph_safe = True
+    graph_safe_portions = True
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.dim, self.vdim = int(p["heads"]), int(p["dim"]), int(p["vdim"])
+        self.cap, self.eps = float(p["gate_cap"]), float(p["eps"])
+        if min(self.heads, self.dim, self.vdim) <= 0 or not self.cap > 0:
+            raise ValueError("heads, dim, vdim and gate_cap must be positive")
+        self.qk, self.inner = self.heads * self.dim, self.heads * self.vdim
+        self.scan_offset = 0
+        self.max_offset = self.heads * (self.vdim + 1) * self.dim  # behind S and n: the running maximum of every head
+
+    def cache_need(self) -> SlotStateNeed:
+        return SlotStateNeed((self.max_offset + self.heads,))
+
+    def tensor_decls(self):
+        h = self.hidden_size
+        for s, out in (("q", self.qk), ("k", self.qk), ("v", self.inner), ("g", self.inner), ("i", self.heads), ("f", self.heads)):
+            yield TensorDecl(self.name(s), (out, h), "matrix", "linear")
+        yield TensorDecl(self.name("i.b"), (self.heads,), "vector", "bias")
+        yield TensorDecl(self.name("f.b"), (self.heads,), "vector", "bias")
+        yield TensorDecl(self.name("norm"), (self.inner,), "vector", "norm")
+        yield TensorDecl(self.name("o"), (h, self.inner), "matrix", "linear")
+
+    def load_weights(self, fetch) -> None:
+        self.w_in = Linear(torch.cat([fetch(self.name(s)) for s in ("q", "k", "v", "g", "i", "f")], dim=0).contiguous())
+        self.bias_i, self.bias_f = fetch(self.name("i.b")).contiguous(), fetch(self.name("f.b")).contiguous()
+        self.norm_w = fetch(self.name("norm")).contiguous()
+        self.o = Linear(fetch(self.name("o")))
+
+    def _gated_output(self, ctx: StepContext, x, view: StateView):
+        qk, inner, h = self.qk, self.inner, self.heads
+        proj = self.w_in.to_float32(x)  # [N, q | k | v | gate | input gate | forget gate], float32
+        at = 2 * qk + 2 * inner
+        coef = rec_ops.gate_scan(proj[:, at : at + h], proj[:, at + h :], self.bias_i, self.bias_f, self.cap, view, self.max_offset, ctx, h)
+        y = rec_ops.recurrence_scan(rec_ops.FORM_GATED_WITH_KEY_SUM, q=proj[:, :qk], k=proj[:, qk : 2 * qk], v=proj[:, 2 * qk : 2 * qk + inner],
+                                    pre=coef, p0=None, p1=None, p2=None, view=view, offset=self.scan_offset, ctx=ctx, heads=h, dk=self.dim,
+                                    dv=self.vdim + 1, q_scale=self.dim ** -0.5)
+        return rec_ops.memory_norm(y, coef[:, 2 * h :], proj[:, 2 * qk + inner : at], self.norm_w, h, self.vdim, self.eps, self.dtype)
+
+    def mix(self, ctx: StepContext, x, view: StateView):
+        return self.o.to_float32(self._gated_output(ctx, x, view))
+
+    def forward(self, ctx: StepContext, x, view: StateView, stream: ResidualStream):
+        return self.o.add_or_defer(self._gated_output(ctx, x, view), stream)
+
+
+register_mixer("channel_delta", ChannelDeltaMixer, replace=True)
+register_mixer("matrix_memory", MatrixMemoryMixer, replace=True)
 register_mixer("gated_linear", GatedLinearMixer, replace=True)
 register_mixer("decay_linear", DecayLinearMixer, replace=True)
 register_mixer("mamba2", Mamba2Mixer, replace=True)

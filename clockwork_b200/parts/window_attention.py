@@ -8,15 +8,23 @@ Parameters: ``hidden_size, heads, kv_heads, dim`` (query/key size per head), ``v
 * ``head_scale``: the score of head h is multiplied by ``temp[h]``;
 * ``talk``: the heads' scores are mixed before they become weights, ``s_h <- sum_g talk[h, g] s_g``;
 * ``head_bias``: ``pb[h]`` is added to the (mixed) score;
-* ``weights``: ``"softmax"`` over the visible keys, or ``"sigmoid"`` of each score on its own (not normalised).
+* ``weights``: ``"softmax"`` over the visible keys, or ``"sigmoid"`` of each score on its own (not normalised);
+* ``mask``: ``"window"`` (the default: the last ``window`` positions) or ``"block"``: positions are cut into blocks of
+  ``window`` counted from the start of the sequence, and position t sees the positions j <= t of its own block;
+* ``sink``: the softmax's denominator also holds ``exp(sink[h])``, a learned logit per head without key or value
+  (tensor ``sink`` [heads]);
+* ``rotary``: ``{"dims", "base"}``: the first ``dims`` entries of every query and key head are rotated by the token's
+  position before the key is cached, entry i with entry i + dims/2 by the angle ``t * base^(-2i/dims)`` (float32).
 
-Positions do not enter the scores.  Tensors: ``q`` [heads*dim, hidden], ``k`` [kv_heads*dim, hidden], ``v``
+Without ``rotary`` positions do not enter the scores.  Tensors: ``q`` [heads*dim, hidden], ``k`` [kv_heads*dim, hidden], ``v``
 [kv_heads*vdim, hidden], ``o`` [hidden, heads*vdim], and those the switches name.
 
 The cache keeps one row ``[key | value]`` per token and key/value head (``PagedKVNeed(planes=1)`` with rows of
 ``dim + vdim``), in a page group that gives pages back behind the window.  At load the rows of k and v are
 interleaved head by head behind q, so that one product yields ``[q | k_0 v_0 | k_1 v_1 ..]`` per token and the
-cache write is a copy of the row's tail.  Scores, weights and weighted sums are float32 in either run precision.
+cache write is a copy of the row's tail (with ``rotary`` the product's output is float32 and one kernel rotates,
+rounds once and stores).  A blocked layer's page group gives back the pages of blocks that have passed.
+Scores, weights and weighted sums are float32 in either run precision.
 """
 
 from __future__ import annotations
@@ -47,6 +55,18 @@ class WindowAttention(Mixer):
         self.weights = str(p.get("weights", "softmax"))
         if self.weights not in ("softmax", "sigmoid"):
             raise ValueError(f"weights must be 'softmax' or 'sigmoid', got {self.weights!r}")
+        self.mask = str(p.get("mask", "window"))
+        if self.mask not in ("window", "block"):
+            raise ValueError(f"mask must be 'window' or 'block', got {self.mask!r}")
+        self.has_sink = bool(p.get("sink", False))
+        if self.has_sink and self.weights != "softmax":
+            raise ValueError("a sink belongs to softmax weights")
+        rotary = p.get("rotary")
+        self.rot_dims = int(rotary["dims"]) if rotary else 0
+        self.rot_base = float(rotary["base"]) if rotary else 0.0
+        if rotary and (self.rot_dims <= 0 or self.rot_dims % 2 or self.rot_dims > int(p["dim"]) or self.rot_base <= 0):
+            raise ValueError(f"rotary dims {self.rot_dims} must be even, positive and at most dim {p['dim']}, the base positive")
+        self.inv_freq = self.sink = None
         if self.heads <= 0 or self.kv_heads <= 0 or self.heads % self.kv_heads:
             raise ValueError(f"heads {self.heads} not a multiple of kv_heads {self.kv_heads}")
         if min(self.dim, self.vdim, self.window) <= 0:
@@ -57,6 +77,8 @@ class WindowAttention(Mixer):
         self.head_scale = self.talk = self.head_bias = None
 
     def cache_need(self) -> PagedKVNeed:
+        if self.mask == "block":
+            return PagedKVNeed(self.kv_heads, self.row, None, planes=1, block=self.window)
         return PagedKVNeed(self.kv_heads, self.row, self.window, planes=1)
 
     def reserve_for_steps(self, max_seqs: int, max_ctx: int) -> None:
@@ -75,6 +97,8 @@ class WindowAttention(Mixer):
             yield TensorDecl(self.name("talk"), (self.heads, self.heads), "vector", "norm")
         if self.has_head_bias:
             yield TensorDecl(self.name("pb"), (self.heads,), "vector", "bias")
+        if self.has_sink:
+            yield TensorDecl(self.name("sink"), (self.heads,), "vector", "bias")
         yield TensorDecl(self.name("o"), (h, self.heads * self.vdim), "matrix", "linear")
         if self.bias:
             yield TensorDecl(self.name("o.b"), (h,), "vector", "bias")
@@ -100,16 +124,28 @@ class WindowAttention(Mixer):
             self.talk = fetch(self.name("talk")).contiguous()
         if self.has_head_bias:
             self.head_bias = fetch(self.name("pb")).contiguous()
+        if self.has_sink:
+            self.sink = fetch(self.name("sink")).contiguous()
+        if self.rot_dims:
+            # base^(-2i/dims) worked out in float64 and rounded once
+            i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+            self.inv_freq = (self.rot_base ** (-2.0 * i / self.rot_dims)).to(torch.float32).to(self.qkv.weight.device)
 
     def _attend(self, ctx: StepContext, x: torch.Tensor, view: PagedView) -> torch.Tensor:
-        qkv = self.qkv(x)  # [N, heads*dim | kv_heads*(dim + vdim)]
         rows = view.k_cache  # [pages, page_size, kv_heads, dim + vdim]
-        if view.write:
-            window_ops.store_rows(qkv, self.heads * self.dim, self.kv_heads * self.row, rows, view.slots, ctx.status)
+        if self.rot_dims:
+            # the product in float32, so that rotated queries and keys are rounded to the run's precision once
+            q = window_ops.rotate_store(self.qkv.to_float32(x), ctx.positions, ctx.tok_seq, view.slots if view.write else None,
+                                        self.inv_freq, self.heads, self.kv_heads, self.dim, self.vdim, self.rot_dims, rows, ctx.status)
+        else:
+            q = self.qkv(x)  # [N, heads*dim | kv_heads*(dim + vdim)]
+            if view.write:
+                window_ops.store_rows(q, self.heads * self.dim, self.kv_heads * self.row, rows, view.slots, ctx.status)
         parts = window_ops.window_parts(ctx.num_tokens, self.window, self.dtype)
-        return window_ops.window_attention(qkv, rows, view.block_tables, ctx.positions, ctx.tok_seq, ctx.q_start, self.heads, self.kv_heads,
+        return window_ops.window_attention(q, rows, view.block_tables, ctx.positions, ctx.tok_seq, ctx.q_start, self.heads, self.kv_heads,
                                            self.dim, self.vdim, self.window, self.scale, self.head_scale, self.talk,
-                                           self.head_bias, self.weights == "sigmoid", ctx.status, parts)
+                                           self.head_bias, self.weights == "sigmoid", ctx.status, parts,
+                                           blocked=self.mask == "block", sink=self.sink)
 
     def mix(self, ctx: StepContext, x: torch.Tensor, view: PagedView) -> torch.Tensor:
         return self.o.to_float32(self._attend(ctx, x, view))
