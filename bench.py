@@ -370,8 +370,12 @@ def compare_designs(args) -> int:
     With ``--design gamesun`` the design is Gamesun (``gamesun-2k``: windowed attention of 16 heads of 128 on 4
     key/value heads beside linear attention of 16 heads, windows of 4,096 and 1,024, gated feed-forwards of 7,168)
     beside a Qwen2 decoder of the same width, heads, layer count and feed-forward; ``--prompt-len`` sets the context
-    that the single-token steps run behind.  With ``--layers N`` both models have N layers.  One JSON line; device
-    time by CUDA events, medians."""
+    that the single-token steps run behind.  With ``--design kapolorn`` the design is Kapolorn (``kapolorn-2k``: attention
+    over blocks of 1,024 positions with rotation and a sink beside a matrix memory, a delta-rule layer in every fourth
+    place, 32 routed experts of which a token uses 4 and a shared one, 7,168 feed-forward rows a token in all) beside
+    Gamesun, the closest design the framework has (``gamesun-2k``: the same width, heads and layer count, two mixers side
+    by side in every layer, a gated feed-forward of 7,168).  With ``--layers N`` both models have N layers.  One JSON
+    line; device time by CUDA events, medians."""
     import torch
 
     from clockwork_b200.cache import CacheManager
@@ -380,7 +384,7 @@ def compare_designs(args) -> int:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(0)
-    shape = {"rapitar": "rapitar-2k", "gamesun": "gamesun-2k"}[args.design]
+    shape = {"rapitar": "rapitar-2k", "gamesun": "gamesun-2k", "kapolorn": "kapolorn-2k"}[args.design]
     rapitar = shape_config(shape, args.layers)
     layers = len(rapitar["layers"])
     qwen = dict(QWEN25_1P5B, num_hidden_layers=layers, hidden_size=2048, num_attention_heads=16,
@@ -389,7 +393,10 @@ def compare_designs(args) -> int:
     rng = random.Random(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")  # larger than L2: written between timed calls
     out = {"impl": "ours", "layers": layers, "width": 2048, "dtype": "bf16", "data": "synthetic", "l2": "flushed between timed calls"}
-    for name, raw, vocab in ((shape, rapitar, rapitar["vocab"]), ("qwen2-2k", qwen, qwen["vocab_size"])):
+    beside = ("qwen2-2k", qwen, qwen["vocab_size"])
+    if args.design == "kapolorn":
+        beside = ("gamesun-2k", shape_config("gamesun-2k", layers), rapitar["vocab"])
+    for name, raw, vocab in ((shape, rapitar, rapitar["vocab"]), beside):
         if args.model_filter and args.model_filter not in name:
             continue
         model = random_model(raw, seed=0, dtype="bfloat16", device="cuda:0")
@@ -456,7 +463,7 @@ def main() -> int:
     ap.add_argument("--top-k", type=int, default=-1)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (reported in config)")
-    ap.add_argument("--design", choices=["rapitar", "gamesun"], default="rapitar", help="with --only designs: which design stands beside Qwen2")
+    ap.add_argument("--design", choices=["rapitar", "gamesun", "kapolorn"], default="rapitar", help="with --only designs: which design stands beside Qwen2")
     ap.add_argument("--model-filter", default="", help="with --only designs: run only the model whose name holds this text (profiling runs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="qwen2.5-1.5b",

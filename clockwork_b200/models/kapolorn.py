@@ -50,9 +50,9 @@ class KapolornConfig:
 def _layers_2k(repeats: int) -> list:
     """Layer sizes of a model of 2,048 width: attention of 16 heads of 128 on 4 key/value heads over blocks of 1,024
     positions beside a matrix memory of 16 heads of 64 x 128; a delta-rule layer of 16 heads of 128 x 128; 32 experts of
-    1,408 in 4 groups, of which 4 of the best 2 groups, and a shared expert of 2,816."""
+    1,408 in 4 groups, of which 4 of the best 2 groups, and a shared expert of 1,536 (a token goes through 7,168 rows)."""
     moe = {"kind": "moe", "expert": {"ff": 1408, "limit": 7.0},
-           "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": 2816, "limit": 7.0}}
+           "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": 1536, "limit": 7.0}}
     pair = {"type": "parallel", "mlp": moe, "mixer": {
         "left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
                  "rot": {"dims": 64, "base": 10000.0}},

@@ -199,23 +199,44 @@ def clamped_expert(h, w, p, limit, rnd=exact):
 
 
 def route(h, w, p, r):
-    """(chosen experts [T, top], their weights [T, top])."""
+    """(chosen experts [T, top], their weights [T, top], how far every token's choice is from another one [T]: the
+    smallest gap, in router logits, between something taken and the best thing left out, among groups and among the
+    allowed experts; infinite where nothing is left out)."""
     experts, top = r["experts"], r["top"]
-    count, keep = r["groups"]["count"], r["groups"]["keep"]
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    count, keep = groups["count"], groups["keep"]
     scores = torch.softmax(h @ w[f"{p}.router"].T, dim=-1)
     best = scores.reshape(-1, count, experts // count).max(-1).values
     kept = torch.zeros_like(best, dtype=torch.bool).scatter(-1, best.topk(keep, dim=-1).indices, True)
     allowed = kept.repeat_interleave(experts // count, dim=-1)
-    chosen = scores.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
-    return chosen, scores.gather(-1, chosen)
+    ranked = scores.masked_fill(~allowed, -1.0)
+    chosen = ranked.topk(top, dim=-1).indices
+    margin = torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    if keep < count:
+        order = best.sort(dim=-1, descending=True).values
+        margin = torch.minimum(margin, torch.log(order[:, keep - 1] / order[:, keep]))
+    if top < keep * (experts // count):
+        order = ranked.sort(dim=-1, descending=True).values
+        margin = torch.minimum(margin, torch.log(order[:, top - 1] / order[:, top]))
+    return chosen, scores.gather(-1, chosen), margin
 
 
-def mixture_of_experts(h, w, p, m, rnd=exact):
-    chosen, weights = route(h, w, p, m["router"])
-    out = clamped_expert(h, w, f"{p}.shared", m["shared"]["limit"], rnd)
+def mixture_of_experts(h, w, p, m, rnd=exact, forced=None, log=None):
+    """``forced``: the experts to use (the weights are still this run's scores of them); ``log``: a list that receives
+    (chosen, margin) of this call."""
+    chosen, weights, margin = route(h, w, p, m["router"])
+    if log is not None:
+        log.append((chosen, margin))
+    if forced is not None:
+        chosen = forced
+        weights = torch.softmax(h @ w[f"{p}.router"].T, dim=-1).gather(-1, chosen)
+    if m.get("shared") is not None:
+        out = clamped_expert(h, w, f"{p}.shared", m["shared"]["limit"], rnd)
+    else:
+        out = torch.zeros_like(h)
     for e in range(m["router"]["experts"]):
         share = (weights * (chosen == e)).sum(-1, keepdim=True)
-        rows = share[:, 0] > 0
+        rows = (chosen == e).any(-1)
         if rows.any():
             out[rows] = out[rows] + share[rows] * clamped_expert(h[rows], w, f"{p}.e{e}", m["expert"]["limit"], rnd)
     return out
@@ -230,23 +251,28 @@ def mixer_of(layer, h, w, p, eps, rnd=exact):
     raise ValueError(layer["type"])
 
 
-def forward(config, weights, tokens, dtype=torch.float64, rnd=exact, keep_layers=False):
-    """Logits [T, vocab] of one whole sequence (and, with ``keep_layers``, the residual after every layer run)."""
+def forward(config, weights, tokens, dtype=torch.float64, rnd=exact, keep_layers=False, routes=None, log=None):
+    """Logits [T, vocab] of one whole sequence (and, with ``keep_layers``, the residual after every layer run).
+    ``log``: a list that receives (chosen experts, margin) of every feed-forward run, in run order; ``routes``: such a
+    list of an earlier call, whose choices this call then uses instead of its own (the yardstick of a rounded run that
+    must not count a choice that rounding flipped)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = config["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)] * config["embedding"]["scale"]
-    kept = []
+    kept, ff_run = [], 0
     for i, _ in run_order(config):
         layer = config["layers"][i]
         h = rnd(scaled_norm(x, w[f"l{i}.norm1"], eps))
         x = x + scaled_norm(mixer_of(layer, h, w, f"l{i}.mix", eps, rnd), w[f"l{i}.norm1b"], eps)
         if layer.get("mlp") is not None:
             h = rnd(scaled_norm(x, w[f"l{i}.norm2"], eps))
-            x = x + scaled_norm(mixture_of_experts(h, w, f"l{i}.mlp", layer["mlp"], rnd), w[f"l{i}.norm2b"], eps)
+            forced = routes[ff_run][0] if routes is not None else None
+            x = x + scaled_norm(mixture_of_experts(h, w, f"l{i}.mlp", layer["mlp"], rnd, forced, log), w[f"l{i}.norm2b"], eps)
+            ff_run += 1
         kept.append(x)
     z = rnd(scaled_norm(x, w["final.norm"], eps)) @ w["embed"].T
-    cap = config["logit_softcap"]
-    logits = cap * torch.tanh(z / cap)
+    cap = config.get("logit_softcap")
+    logits = z if cap is None else cap * torch.tanh(z / cap)
     return (logits, torch.stack(kept)) if keep_layers else logits
 
 
