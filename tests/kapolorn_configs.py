@@ -51,7 +51,7 @@ def _model(vocab, width, eps, scale, cap, loop, layers):
 
 
 CONFIG_A = _model(96, 64, 1e-5, 2.0, 12.0, (1, 2, 3), [
-    (_pair(4, 2, 24, 12, 21, 0.3, 8, 1000.0, 3, 20, 12, 8.0, 0.7, 1.3), _moe(40, 1.5, 6, 2, (3, 2), (56, 2.5))),
+    (_pair(4, 2, 24, 12, 21, 0.3, 8, 1000.0, 3, 20, 12, 8.0, 0.7, 1.3), _moe(40, 1.5, 6, 3, (3, 2), (56, 2.5))),
     (_delta(4, 2, 12, 20, 3), _moe(24, 1.0, 4, 1, (2, 1), (16, 1.0))),
     (_pair(3, 1, 16, 40, 7, 0.25, 16, 50000.0, 1, 24, 8, 15.0, 1.0, 1.0), None),
 ])
