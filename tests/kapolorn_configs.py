@@ -145,14 +145,52 @@ def draw_weights(config: dict, rank: int, seed: int) -> dict[str, torch.Tensor]:
     return out
 
 
-def write_model(folder, name: str, seed: int = 0) -> Path:
+ROUTING_CLASSES = 8
+
+
+def steady_routing(config: dict, weights: dict[str, torch.Tensor], seed: int = 0, step: float = 0.5) -> dict[str, torch.Tensor]:
+    """Router choices that rounding cannot flip, for runs in bfloat16 that are compared with a run that rounds
+    elsewhere.  The first ``ROUTING_CLASSES`` coordinates of the residual become a one-hot code of token mod classes (4
+    after the embedding's scale) that no layer writes to (the output norms' weights are 0 there), and every router
+    reads, for each class, a permutation of the levels 0, step, 2 step .. from that class's coordinate, besides a
+    thirtieth of its drawn weights on the others.  Router logits are then (4 / rms(x)) times distinct levels plus a
+    small part that depends on the context: the order, among groups and among experts, is the class's permutation, and
+    the scores still fall off slowly enough that every chosen expert counts."""
+    c = ROUTING_CLASSES
+    gen = torch.Generator().manual_seed(1000 + seed)
+    out = dict(weights)
+    embed = weights["embed"].float().clone()
+    embed[:, :c] = 0.0
+    rows = torch.arange(embed.shape[0])
+    embed[rows, rows % c] = 4.0 / config["embedding"]["scale"]
+    out["embed"] = embed.to(torch.bfloat16)
+    for i, layer in enumerate(config["layers"]):
+        for name in (f"l{i}.norm1b", f"l{i}.norm2b"):
+            if name in weights:
+                t = weights[name].clone()
+                t[:c] = 0.0
+                out[name] = t
+        if layer["mlp"] is not None:
+            norm = weights[f"l{i}.norm2"].clone()
+            norm[:c] = 1.0
+            out[f"l{i}.norm2"] = norm
+            router = weights[f"l{i}.mlp.router"].float() / 30.0
+            experts = router.shape[0]
+            for k in range(c):
+                router[:, k] = step * torch.randperm(experts, generator=gen).float()
+            out[f"l{i}.mlp.router"] = router.to(torch.bfloat16)
+    return out
+
+
+def write_model(folder, name: str, seed: int = 0, steady: bool = False) -> Path:
     from clockwork_b200.weights import save_safetensors
 
     config, _, rank = CONFIGS[name]
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     (folder / "config.json").write_text(json.dumps(config))
-    save_safetensors(folder / "model.safetensors", draw_weights(config, rank, seed))
+    weights = draw_weights(config, rank, seed)
+    save_safetensors(folder / "model.safetensors", steady_routing(config, weights, seed) if steady else weights)
     return folder
 
 

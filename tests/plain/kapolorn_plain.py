@@ -276,6 +276,40 @@ def forward(config, weights, tokens, dtype=torch.float64, rnd=exact, keep_layers
     return (logits, torch.stack(kept)) if keep_layers else logits
 
 
+def first_position_margin(config, weights, token, dtype=torch.float64):
+    """At position 0 a head of the matrix memory and of the delta rule puts out (k . q) times a positive number times v,
+    and its norm makes sign(k . q) n(v) of that: the smallest |cos(q, k)| over those heads, in every layer run, says how
+    far the first token is from a sign that rounding could flip."""
+    w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
+    eps = config["norm"]["eps"]
+    x = w["embed"][torch.as_tensor([token], dtype=torch.long)] * config["embedding"]["scale"]
+    margin = 1.0
+
+    def cosine(q, k):
+        return float(((q * k).sum(-1) / (q.norm(dim=-1) * k.norm(dim=-1))).abs().min())
+
+    for i, _ in run_order(config):
+        layer, p = config["layers"][i], f"l{i}.mix"
+        h = scaled_norm(x, w[f"l{i}.norm1"], eps)
+        if layer["type"] == "parallel":
+            m = layer["mixer"]["right"]
+            q, k = ((h @ w[f"{p}.right.{s}"].T).reshape(m["heads"], m["dim"]) for s in "qk")
+        else:
+            m = layer["mixer"]  # one row: the convolution leaves the current token's tap
+            q, k = (F.silu((h @ w[f"{p}.{s}"].T) * w[f"{p}.{s}.conv"][:, -1]).reshape(m["kv_heads"], m["dim"]) for s in "qk")
+        margin = min(margin, cosine(q, k))
+        x = x + scaled_norm(mixer_of(layer, h, w, p, eps), w[f"l{i}.norm1b"], eps)
+        if layer.get("mlp") is not None:
+            h = scaled_norm(x, w[f"l{i}.norm2"], eps)
+            x = x + scaled_norm(mixture_of_experts(h, w, f"l{i}.mlp", layer["mlp"]), w[f"l{i}.norm2b"], eps)
+    return margin
+
+
+def steady_first_token(config, weights, candidates=range(40)):
+    """The candidate whose answer at position 0 is farthest from such a flip."""
+    return max(candidates, key=lambda token: first_position_margin(config, weights, token))
+
+
 def greedy_generate(config, weights, prompt, count, dtype=torch.float64):
     tokens = list(prompt)
     for _ in range(count):
