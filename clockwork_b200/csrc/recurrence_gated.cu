@@ -249,54 +249,73 @@ extern "C" int cw_delta_scan(const float* q, int ldq, const float* k, int ldk, c
 // ---- the gates of a matrix memory -----------------------------------------------------------------------
 // zi, zf [N, ld*] float32 pre-activations of the input and forget gates (a column per head); the running maximum m of
 // every head is one float of the request's state (at state_off + h; 0 when a request starts).  coef [N, 3H].
-// A block per request: first every (token, head) pair's two logarithms side by side, then a thread per head walks the
-// tokens in order (a chain of one addition and one maximum per token).
-__global__ void __launch_bounds__(128)
+// A block per request, GS_WORDS / H tokens at a time through shared memory, in three passes: every (token, head) pair's
+// two logarithms side by side; a thread per head walks the tokens in order (a chain of one addition and one maximum
+// per token, its operands already on chip, so a token costs a few cycles); every pair's three exponentials side by
+// side.  The chain's order is the tokens' order whatever the cut, so a request's coefficients do not depend on how
+// its tokens came in steps.
+#define GS_WORDS 2048
+__global__ void __launch_bounds__(1024)
 gate_scan_kernel(const float* __restrict__ zi, int ldi, const float* __restrict__ zf, int ldf, const float* __restrict__ bias_i,
                  const float* __restrict__ bias_f, float cap, float* __restrict__ state, long long state_stride, long long state_off,
                  const long long* __restrict__ slots, const int* __restrict__ tok_seq, const int* __restrict__ q_start, int H,
                  float* __restrict__ coef) {
+    __shared__ float s_li[GS_WORDS], s_lf[GS_WORDS], s_m[2 * GS_WORDS];  // s_m: the maximum before token t at [t][h], after it at [t+1][h]
     pdl_wait();
     const int seq = blockIdx.x;
     const int start = q_start[seq], end = q_start[seq + 1];
     if (end <= start) return;
-    const int n = end - start;
     const size_t ldc = 3 * (size_t)H;
     if (tok_seq[start] < 0) {  // padding rows: coefficients that leave a zero state at zero
+        const int n = end - start;
         for (int idx = threadIdx.x; idx < n * 3 * H; idx += blockDim.x) coef[(size_t)start * ldc + idx] = idx % (3 * H) < 2 * H ? 0.f : 1.f;
         return;
     }
-    for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
-        const int t = start + idx / H, h = idx % H;
-        const float li = cap * tanhf((zi[(size_t)t * ldi + h] + (bias_i != nullptr ? bias_i[h] : 0.f)) / cap);
-        const float c = cap * tanhf((zf[(size_t)t * ldf + h] + (bias_f != nullptr ? bias_f[h] : 0.f)) / cap);
-        const float lf = fminf(c, 0.f) - log1pf(expf(-fabsf(c)));
-        coef[(size_t)t * ldc + h] = li;
-        coef[(size_t)t * ldc + H + h] = lf;
-    }
-    __syncthreads();
     float* m_mem = state + slots[seq] * state_stride + state_off;
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float m = m_mem[h];
-        for (int t = start; t < end; ++t) {
-            float* c = coef + (size_t)t * ldc;
-            const float li = c[h], lf = c[H + h];
-            const float m_new = fmaxf(lf + m, li);
-            c[h] = expf(lf + m - m_new);
-            c[H + h] = expf(li - m_new);
-            c[2 * H + h] = expf(-m_new);
-            m = m_new;
+    const int TC = GS_WORDS / H;  // (the launcher refuses more heads than GS_WORDS)
+    for (int c0 = start; c0 < end; c0 += TC) {
+        const int n = min(TC, end - c0);
+        for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
+            const int t = c0 + idx / H, h = idx % H;
+            const float li = cap * tanhf((zi[(size_t)t * ldi + h] + (bias_i != nullptr ? bias_i[h] : 0.f)) / cap);
+            const float c = cap * tanhf((zf[(size_t)t * ldf + h] + (bias_f != nullptr ? bias_f[h] : 0.f)) / cap);
+            s_li[idx] = li;
+            s_lf[idx] = fminf(c, 0.f) - log1pf(expf(-fabsf(c)));
         }
-        m_mem[h] = m;
+        __syncthreads();
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            float m = m_mem[h];
+            s_m[h] = m;
+#pragma unroll 8
+            for (int t = 0; t < n; ++t) {
+                m = fmaxf(s_lf[t * H + h] + m, s_li[t * H + h]);
+                s_m[(t + 1) * H + h] = m;
+            }
+            m_mem[h] = m;
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < n * H; idx += blockDim.x) {
+            const int t = idx / H, h = idx - t * H;
+            const float before = s_m[idx], after = s_m[idx + H];
+            float* c = coef + (size_t)(c0 + t) * ldc;
+            c[h] = expf(s_lf[idx] + before - after);
+            c[H + h] = expf(s_li[idx] - after);
+            c[2 * H + h] = expf(-after);
+        }
+        __syncthreads();  // the next chunk writes the same shared memory
     }
 }
 
+// N: the rows of the step (all requests'), which only sizes the blocks.
 extern "C" int cw_gate_scan(const float* zi, int ldi, const float* zf, int ldf, const float* bias_i, const float* bias_f, float cap,
                             float* state, long long state_stride, long long state_off, const long long* slots, const int* tok_seq,
-                            const int* q_start, int S, int H, float* coef, cudaStream_t stream) {
+                            const int* q_start, int S, int H, int N, float* coef, cudaStream_t stream) {
     if (S == 0) return CW_OK;
     if (S < 0 || H <= 0 || ldi < H || ldf < H || !(cap > 0.f)) return CW_ERR_BAD_SIZE;
-    return cw_launch_ordered(gate_scan_kernel, dim3(S), dim3(128), 0, stream, zi, ldi, zf, ldf, bias_i, bias_f, cap, state, state_stride,
+    if (H > GS_WORDS) return CW_ERR_UNSUPPORTED;
+    const long long per_request = (long long)(N > 0 ? N : S) * H / S;  // pairs of a request, if the rows were spread evenly
+    const int threads = per_request >= 8192 ? 1024 : per_request >= 1024 ? 256 : 128;
+    return cw_launch_ordered(gate_scan_kernel, dim3(S), dim3(threads), 0, stream, zi, ldi, zf, ldf, bias_i, bias_f, cap, state, state_stride,
                              state_off, slots, tok_seq, q_start, H, coef);
 }
 

@@ -61,7 +61,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_unit_heads": [P, I, I, I, I, F, I, F, F, P],
     "cw_delta_coefficients": [P, I, P, P, P, I, I, I, I, P],
     "cw_delta_scan": [P, I, P, I, P, I, P, I, P, I, P, LL, LL, P, P, P, I, I, I, I, I, P, I, P],
-    "cw_gate_scan": [P, I, P, I, P, P, F, P, LL, LL, P, P, P, I, I, P, P],
+    "cw_gate_scan": [P, I, P, I, P, P, F, P, LL, LL, P, P, P, I, I, I, P, P],
     "cw_memory_norm": [P, P, I, P, I, P, P, I, I, I, F, I, P],
     # attention over a cached latent (csrc/latent_attention.cu)
     "cw_latent_prepare": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, I, P, P],

@@ -154,7 +154,7 @@ def gate_scan(zi: torch.Tensor, zf: torch.Tensor, bias_i: torch.Tensor | None, b
     state, stride, slots = _state_args(view)
     check(library().cw_gate_scan(_ptr(zi), zi.stride(0) if n > 1 else max(zi.stride(0), heads), _ptr(zf),
                                  zf.stride(0) if n > 1 else max(zf.stride(0), heads), _ptr(bias_i), _ptr(bias_f), float(cap), state, stride,
-                                 offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start), ctx.num_seqs, heads, _ptr(coef), _stream()), "gate_scan")
+                                 offset, slots, _ptr(ctx.tok_seq), _ptr(ctx.q_start), ctx.num_seqs, heads, n, _ptr(coef), _stream()), "gate_scan")
     return coef
 
 
