@@ -67,7 +67,20 @@ struct GemmParams {
     bf16* emit_x;             // [T, N]
     float* emit_part;         // [T, gridDim.x]
     int* split_flags;         // CTA-pair kernel with splits > 1: two words per tile, zero between launches
+    float act_limit;          // SWIGLU only.  0: silu(gate) * up.  Positive: the clamped form (gated_act)
 };
+
+// What the gated kernels make of the two accumulators.  limit 0: silu(g) * u.  limit > 0: with a = min(g, limit) and
+// b = clamp(u, -limit, limit), a * sigmoid(1.702 a) * (b + 1).  The fast exponential and division: the result is rounded
+// to bfloat16 (8 bits) right after, their 2^-21 relative error does not show.  (limit is the same for a whole launch.)
+__device__ __forceinline__ float gated_act(float g, float u, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        return __fdividef(g, 1.0f + __expf(-1.702f * g)) * u;
+    }
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
 
 #include "gemm_tc_pair.cuh"
 
@@ -310,7 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int j = 0; j < 16; ++j) {
                 const float sc = scaled ? inv_s[c + j] : 1.0f;
                 float v = g[j] * sc + bias;
-                if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * (u[j] * sc);
+                if (SWIGLU) v = gated_act(v, u[j] * sc, p.act_limit);
                 if (wide)
                     stage[(c + j) * BM + row] = v;
                 else
@@ -366,12 +379,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 float* c32 = (float*)p.C + (size_t)t_base * p.ldc + f;
                 bf16* c16 = (bf16*)p.C + (size_t)t_base * p.ldc + f;
                 if (SWIGLU) {
-                    // silu(v) * u with the fast exponential and division: the result is rounded to
-                    // bfloat16 (8 bits) right after, their 2^-21 relative error does not show
 #pragma unroll
                     for (int j = 0; j < NC; ++j)
                         if (j < ncols && t_base + j < p.T)
-                            c16[(size_t)j * p.ldc] = __float2bfloat16_rn(__fdividef(g[j], 1.0f + __expf(-g[j])) * u[j]);
+                            c16[(size_t)j * p.ldc] = __float2bfloat16_rn(gated_act(g[j], u[j], p.act_limit));
                 } else if (p.epilogue == 0) {
 #pragma unroll
                     for (int j = 0; j < NC; ++j)
@@ -642,7 +653,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     float v = g[j] + bias;
-                    if (SWIGLU) v = __fdividef(v, 1.0f + __expf(-v)) * u[j];
+                    if (SWIGLU) v = gated_act(v, u[j], p.act_limit);
                     if (wide)
                         st32[j * BM + row] = v;
                     else
@@ -950,17 +961,16 @@ extern "C" int cw_gemm_tc_plan(int T, int N, int K, int swiglu, int sm_count, in
 // product finishes a norm whose un-normalised, weight-multiplied rows it got as X; with `emit_x`
 // (epilogue 1 only) it begins the norm that follows it.  Both need at most 128 tokens
 // (CW_ERR_UNSUPPORTED otherwise).
-extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
-                               int N, int K, int ldx, int ldc, int epilogue, int sm_count,
-                               const float* scale_part, int scale_parts, float scale_eps, int scale_dim,
-                               const float* emit_g, void* emit_x, float* emit_part, int* status,
-                               cudaStream_t stream);
+static int gemm_tc_run(const void* X, const void* W, const void* W2, const float* bias, void* C, int T, int N, int K, int ldx,
+                       int ldc, int epilogue, int sm_count, const float* scale_part, int scale_parts, float scale_eps,
+                       int scale_dim, const float* emit_g, void* emit_x, float* emit_part, float act_limit, int* status,
+                       cudaStream_t stream);
 
 extern "C" int cw_gemm_tc(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
                           int N, int K, int ldx, int ldc, int epilogue, int sm_count, int* status,
                           cudaStream_t stream) {
-    return cw_gemm_tc_norm(X, W, W2, bias, C, T, N, K, ldx, ldc, epilogue, sm_count, nullptr, 0, 0.f, 1, nullptr,
-                           nullptr, nullptr, status, stream);
+    return gemm_tc_run(X, W, W2, bias, C, T, N, K, ldx, ldc, epilogue, sm_count, nullptr, 0, 0.f, 1, nullptr, nullptr, nullptr,
+                       0.f, status, stream);
 }
 
 extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, const float* bias, void* C, int T,
@@ -968,6 +978,22 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
                                const float* scale_part, int scale_parts, float scale_eps, int scale_dim,
                                const float* emit_g, void* emit_x, float* emit_part, int* status,
                                cudaStream_t stream) {
+    return gemm_tc_run(X, W, W2, bias, C, T, N, K, ldx, ldc, epilogue, sm_count, scale_part, scale_parts, scale_eps, scale_dim,
+                       emit_g, emit_x, emit_part, 0.f, status, stream);
+}
+
+// C [T, N] bfloat16 = act(X Wg^T, X Wu^T) with the clamped activation of gated_act (limit > 0), or silu(.) * (.) (limit 0).
+extern "C" int cw_gemm_tc_gated(const void* X, const void* Wg, const void* Wu, void* C, int T, int N, int K, int ldx, int ldc,
+                                float limit, int sm_count, int* status, cudaStream_t stream) {
+    if (Wu == nullptr || !(limit >= 0.f)) return CW_ERR_BAD_SIZE;
+    return gemm_tc_run(X, Wg, Wu, nullptr, C, T, N, K, ldx, ldc, 0, sm_count, nullptr, 0, 0.f, 1, nullptr, nullptr, nullptr, limit,
+                       status, stream);
+}
+
+static int gemm_tc_run(const void* X, const void* W, const void* W2, const float* bias, void* C, int T, int N, int K, int ldx,
+                       int ldc, int epilogue, int sm_count, const float* scale_part, int scale_parts, float scale_eps,
+                       int scale_dim, const float* emit_g, void* emit_x, float* emit_part, float act_limit, int* status,
+                       cudaStream_t stream) {
     if (T == 0 || N == 0) return CW_OK;
     if (T < 0 || N < 0 || K <= 0 || ldx < K || ldc < N) return CW_ERR_BAD_SIZE;
     if (epilogue < 0 || epilogue > 2) return CW_ERR_UNSUPPORTED;
@@ -1004,6 +1030,7 @@ extern "C" int cw_gemm_tc_norm(const void* X, const void* W, const void* W2, con
     p.scale_part = scale_part; p.scale_parts = scale_parts; p.scale_eps = scale_eps; p.scale_dim = scale_dim;
     p.emit_g = emit_g; p.emit_x = (bf16*)emit_x; p.emit_part = emit_part;
     p.split_flags = g_split_flags;
+    p.act_limit = act_limit;
     dim3 grid((N + BM - 1) / BM, (T + pl.bn - 1) / pl.bn, pl.splits);
     if (grid.y > 65535) return CW_ERR_BAD_SIZE;
     if (pl.pair) {

@@ -267,7 +267,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     float u[16];
                     tmem_ld16(taddr + C::ACC_STRIDE / 2 + c, u);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) g[j] = __fdividef(g[j], 1.0f + __expf(-g[j])) * u[j];
+                    for (int j = 0; j < 16; ++j) g[j] = gated_act(g[j], u[j], p.act_limit);
                 }
                 if (c + PAIR_CHUNK >= c_end) {
                     // the accumulator has been read out: hand the buffer back to the leader's MMA thread

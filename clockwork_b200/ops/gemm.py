@@ -115,4 +115,16 @@ def swiglu(x, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     return gemm_ref_swiglu(xt, w_gate, w_up)
 
 
+def clamped_gated_tc(x, w_gate: torch.Tensor, w_up: torch.Tensor, limit: float):
+    """``a sigmoid(1.702 a) (b + 1)`` with ``a = min(x Wg^T, limit)``, ``b = clamp(x Wu^T, -limit, limit)`` on the
+    tensor-core kernel, or None when it does not take these tensors (the caller then uses the grouped kernel with one
+    group, which takes every size and both precisions)."""
+    lazy, xt = _plain(x)
+    if lazy is not None:
+        xt = lazy.materialize()
+    if not (_use_tc(xt, w_gate) and w_up.is_contiguous() and w_up.data_ptr() % 16 == 0):
+        return None
+    return _tc.gemm_swiglu(xt, w_gate, w_up, limit=limit)
+
+
 from . import gemm_tc as _gemm_tc_module  # noqa: E402,F401  (registers itself as ``_tc``)

@@ -29,6 +29,8 @@ def _configure() -> None:
     lib.cw_gemm_tc.restype = c_int
     lib.cw_gemm_tc_norm.argtypes = [P, P, P, P, P, I, I, I, I, I, I, I, P, I, c_float, I, P, P, P, P, P]
     lib.cw_gemm_tc_norm.restype = c_int
+    lib.cw_gemm_tc_gated.argtypes = [P, P, P, P, I, I, I, I, I, c_float, I, P, P]
+    lib.cw_gemm_tc_gated.restype = c_int
     lib.cw_gemm_tc_plan.argtypes = [I, I, I, I, I, POINTER(c_int), POINTER(c_int), POINTER(c_int)]
     lib.cw_gemm_tc_plan.restype = c_int
     lib.cw_gemm_tc_parts_plan.argtypes = [I, I, I, I, POINTER(c_int)]
@@ -220,12 +222,27 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, *, 
     return out
 
 
-def gemm_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, row_scale: tuple | None = None) -> torch.Tensor:
+def gemm_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, row_scale: tuple | None = None,
+                limit: float = 0.0) -> torch.Tensor:
+    """bfloat16 [T, N] = silu(x Wg^T) * (x Wu^T); with a positive ``limit`` the clamped form ``a sigmoid(1.702 a) (b + 1)``,
+    ``a = min(x Wg^T, limit)``, ``b = clamp(x Wu^T, -limit, limit)`` (not together with ``row_scale``)."""
     _need(w_gate, torch.bfloat16, "w_gate", 2)
     _need(w_up, torch.bfloat16, "w_up", 2)
     if w_gate.shape != w_up.shape or w_gate.shape[1] != x.shape[1]:
         raise ValueError("gate and up weights must both be [N, K] with x's K")
     out = torch.empty((x.shape[0], w_gate.shape[0]), dtype=torch.bfloat16, device=x.device)
+    if limit > 0.0:
+        if row_scale is not None:
+            raise ValueError("the clamped activation does not finish a norm")
+        _configure()
+        st = _device_state(x.device)
+        t, k = x.shape
+        ldx = x.stride(0) if t > 1 else max(x.stride(0), k)
+        if ldx % 8:
+            ldx = k
+        check(library().cw_gemm_tc_gated(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), t, w_gate.shape[0], k, ldx, out.stride(0),
+                                         float(limit), st["sms"], _ptr(st["status"]), _stream()), "gemm_tc_gated")
+        return out
     _run(x, w_gate, w_up, None, out, 0, row_scale)
     return out
 

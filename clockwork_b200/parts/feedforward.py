@@ -29,6 +29,7 @@ from __future__ import annotations
 
 import torch
 
+from ..ops import gemm as gemm_ops
 from ..ops import grouped as grouped_ops
 from ..ops import recurrence as rec_ops
 from ..weights.decl import TensorDecl
@@ -124,6 +125,10 @@ class MixtureOfExperts(FeedForward):
         return grouped_ops.expert_down(act, self.w_down, offsets, order), sel, weights
 
     def _shared_act(self, x):
+        if self.shared_limit > 0.0:  # one dense gated product: the tensor-core kernel where it takes the sizes
+            act = gemm_ops.clamped_gated_tc(x, self.shared_gate[0], self.shared_up[0], self.shared_limit)
+            if act is not None:
+                return act
         return grouped_ops.expert_gate_up(x, self.shared_gate, self.shared_up, None, None, 1, self.shared_limit)
 
     def forward(self, ctx: StepContext, x, stream: ResidualStream):

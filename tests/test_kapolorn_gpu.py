@@ -510,6 +510,25 @@ def test_routed_experts_in_groups_with_a_shared_expert_alone(ff, limit, experts,
         at += n
 
 
+@pytest.mark.parametrize("rows, ff, w, limit", [(1, 56, 48, 2.5), (7, 8, 72, 0.7), (150, 192, 320, 1.0), (600, 1536, 512, 7.0), (2100, 256, 1024, 1.5)])
+def test_the_clamped_gated_product_on_the_tensor_cores(rows, ff, w, limit):
+    """The shared expert's first two products with the clamped activation in their epilogue (the tcgen05 kernels: single
+    tokens, split tiles, prompt portions) against float32 arithmetic on the same bfloat16 operands; inputs wide enough
+    that all three clamps bite."""
+    from clockwork_b200.ops import gemm as gemm_ops
+
+    gen = torch.Generator().manual_seed(rows + ff)
+    x = draw(gen, (rows, w), 1.5).to(torch.bfloat16).to(DEV)
+    wg, wu = (draw(gen, (ff, w), 0.7 * limit / (1.5 * w ** 0.5)).to(torch.bfloat16).to(DEV) for _ in range(2))  # products of 0.7 limit
+    got = gemm_ops.clamped_gated_tc(x, wg, wu, limit)
+    assert got is not None and got.dtype == torch.bfloat16
+    a, b = x.float() @ wg.float().T, x.float() @ wu.float().T
+    assert float((a > limit).float().mean()) > 0.02 and float((b.abs() > limit).float().mean()) > 0.04
+    a, b = a.clamp(max=limit), b.clamp(-limit, limit)
+    want = a * torch.sigmoid(1.702 * a) * (b + 1)
+    assert float((got.float() - want).abs().max()) <= 2 ** -8 * float(want.abs().max()) + 1e-3
+
+
 @pytest.mark.parametrize("name, layer", [("A", 0), ("A", 2), ("B", 1), ("B", 2), ("D", 1)])
 def test_the_two_mixers_side_by_side_alone(name, layer):
     """Pages for the one and a state slot for the other in the same layer; the two outputs with their factors."""
