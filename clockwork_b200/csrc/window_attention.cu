@@ -517,6 +517,7 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
             fetch(j0 + WM_BN, stage ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
+            if (args.stages == 1 && t > 0) fetch(j0, 0);  // one stage: everyone left it at the end of the last round
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();  // the tile has landed (and Q, at the first)

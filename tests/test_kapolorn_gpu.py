@@ -342,6 +342,30 @@ def test_blocked_attention_with_rotation_and_a_sink_alone(heads, kv_heads, dim, 
         assert_close(got, want, portions)
 
 
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, block, rot, page", [
+    (4, 4, 256, 256, 100, 128, 16), (8, 8, 256, 256, 64, 128, 64), (16, 1, 64, 64, 4096, 64, 16), (8, 2, 128, 128, 150, 64, 16),
+    (6, 3, 96, 48, 45, 32, 8), (4, 1, 240, 200, 70, 16, 16), (2, 2, 512, 64, 90, 256, 16), (4, 4, 32, 256, 33, 32, 16)])
+def test_blocked_attention_in_bfloat16_at_sizes_that_take_each_arrangement_of_the_tensor_core_kernel(heads, kv_heads, dim, vdim, block, rot, page):
+    """Key/value tiles in two stages and in one (wide heads: blocks of several tiles must fetch every tile), several key/value
+    heads a block and one, wide values; whole and in portions, against the plain implementation in float64; allowed is 3
+    times what rounding q, k, v and the output to bfloat16 costs the plain implementation."""
+    gen = torch.Generator().manual_seed(heads * 100 + block)
+    w, scale = 64, dim ** -0.5
+    t = attention_tensors(gen, w, heads, kv_heads, dim, vdim)
+    wd = {k: v.double() for k, v in t.items()}
+    x = draw(gen, (260, w))
+    m = attention_config(heads, kv_heads, dim, vdim, block, scale, rot, 10000.0)
+    want = plain.blocked_sink_attention(x.double(), wd, "m", m)
+    rounded = plain.blocked_sink_attention(x.double(), wd, "m", m, rnd=plain.to_bfloat16_and_back)
+    allowed = 3 * float((rounded - want).abs().max())
+    assert allowed < 0.1 * float(want.abs().max())
+    part = part_with_weights("mixer", attention_spec(w, heads, kv_heads, dim, vdim, block, scale, rot, 10000.0), "m", torch.bfloat16, t)
+    for portions in ([260], [200] + [1] * 60, [3, 64, 1, 61, 2, 109] + [1] * 20):
+        got = run_mixer(part, x, portions, page_size=page, num_pages=600 // page + 8)
+        worst = float((got.double() - want).abs().max())
+        assert worst <= allowed, f"{portions[:6]}: off by {worst:.3g}, allowed {allowed:.3g}"
+
+
 def test_one_key_that_stands_out_at_either_side_of_a_block_edge():
     """A query and two keys are made so that one score towers over all others, the sink too: the key at the first
     position of the query's block takes the whole softmax, the key one further back (the last of the block before)
