@@ -286,10 +286,21 @@ gate_scan_kernel(const float* __restrict__ zi, int ldi, const float* __restrict_
         for (int h = threadIdx.x; h < H; h += blockDim.x) {
             float m = m_mem[h];
             s_m[h] = m;
-#pragma unroll 8
-            for (int t = 0; t < n; ++t) {
-                m = fmaxf(s_lf[t * H + h] + m, s_li[t * H + h]);
-                s_m[(t + 1) * H + h] = m;
+            for (int t0 = 0; t0 < n; t0 += 8) {  // eight tokens' operands fetched side by side, then the chain through them
+                float li[8], lf[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int at = min(t0 + j, n - 1) * H + h;
+                    li[j] = s_li[at];
+                    lf[j] = s_lf[at];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (t0 + j < n) {
+                        m = fmaxf(lf[j] + m, li[j]);
+                        s_m[(t0 + j + 1) * H + h] = m;
+                    }
+                }
             }
             m_mem[h] = m;
         }
