@@ -455,6 +455,22 @@ def test_matrix_memory_alone(heads, dim, vdim, cap, in_bias):
         assert_close(got, want, portions)
 
 
+@pytest.mark.parametrize("heads, dim, vdim, rows", [(3, 8, 8, 1500), (16, 8, 4, 700), (40, 4, 4, 260), (1, 16, 8, 2300)])
+def test_matrix_memory_over_long_portions(heads, dim, vdim, rows):
+    """The gates' kernel stages a fixed number of (token, head) pairs at a time: portions longer than one stage, for few and
+    many heads, whole and cut where no stage ends, against the plain implementation."""
+    gen = torch.Generator().manual_seed(heads + rows)
+    w = 24
+    t = memory_tensors(gen, w, heads, dim, vdim, 0.5)
+    cfg = dict(heads=heads, dim=dim, vdim=vdim, gate_cap=12.0)
+    part = part_with_weights("mixer", PartSpec("matrix_memory", dict(cfg, hidden_size=w, eps=1e-5)), "m", torch.float32, t)
+    x = draw(gen, (rows, w))
+    want = plain.matrix_memory_mixer(x.double(), {k: v.double() for k, v in t.items()}, "m", cfg, 1e-5)
+    for portions in ([rows], [rows - 701 // heads - 5, 701 // heads, 3, 1, 1]):
+        got = run_mixer(part, x, portions, page_size=16, num_pages=8)
+        assert_close(got, want, portions[:2], rel=1e-4)
+
+
 def delta_tensors(gen, w, heads, kv_heads, dim, vdim, taps, rank):
     conv = lambda rows: draw(gen, (rows, taps), 0.5) + (torch.arange(taps) == taps - 1).float()  # noqa: E731
     return {"m.q": draw(gen, (kv_heads * dim, w), 0.3), "m.k": draw(gen, (kv_heads * dim, w), 0.3), "m.v": draw(gen, (heads * vdim, w), 0.3),
