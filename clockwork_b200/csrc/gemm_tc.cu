@@ -71,15 +71,16 @@ struct GemmParams {
 };
 
 // What the gated kernels make of the two accumulators.  limit 0: silu(g) * u.  limit > 0: with a = min(g, limit) and
-// b = clamp(u, -limit, limit), a * sigmoid(1.702 a) * (b + 1).  The fast exponential and division: the result is rounded
-// to bfloat16 (8 bits) right after, their 2^-21 relative error does not show.  (limit is the same for a whole launch.)
+// b = clamp(u, -limit, limit), a * sigmoid(1.702 a) * (b + 1).  One straight line for both: without a limit the bounds
+// are infinite, the factor 1 and the addend 0, which leave g and u as they are (the three selects do not change within a
+// launch and are worked out once).  The fast exponential and division: the result is rounded to bfloat16 (8 bits) right
+// after, their 2^-21 relative error does not show.
 __device__ __forceinline__ float gated_act(float g, float u, float limit) {
-    if (limit > 0.f) {
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
-        return __fdividef(g, 1.0f + __expf(-1.702f * g)) * u;
-    }
-    return __fdividef(g, 1.0f + __expf(-g)) * u;
+    const bool clamped = limit > 0.f;
+    const float bound = clamped ? limit : INFINITY, steep = clamped ? 1.702f : 1.0f, shift = clamped ? 1.0f : 0.0f;
+    g = fminf(g, bound);
+    u = fminf(fmaxf(u, -bound), bound) + shift;
+    return __fdividef(g, 1.0f + __expf(-(steep * g))) * u;
 }
 
 #include "gemm_tc_pair.cuh"
