@@ -10,8 +10,11 @@ watermark (``:31-36``), growth by one slot with copy-on-write of a shared tail p
 What is added: layers are sorted into *groups* by what their mixer keeps (``PagedKVNeed``: KV
 head count, head size, window).  Each group has its own pool, allocator and per-request block
 table, so layers that keep every key and layers that keep a window of them never share pages;
-a windowed group gives pages back as soon as the window has passed them.  Mixers that keep a
-state of fixed size (``SlotStateNeed``) get a row per request in a slot tensor instead of pages.
+a windowed group gives pages back as soon as the window has passed them.  A group may keep one
+row per ``every`` positions instead of one per position (``PagedKVNeed.every``: summaries of whole
+blocks of positions); its tables are that much shorter and its pool that much smaller.  Mixers that
+keep a state of fixed size (``SlotStateNeed``) get a row per request in a slot tensor instead of
+pages.  A mixer may name several needs (a tuple): pages of one or two kinds and a state slot.
 """
 
 from __future__ import annotations
@@ -33,6 +36,7 @@ class PageGroup:
     def __init__(self, need: PagedKVNeed, cache_layers: list[int], num_pages: int, page_size: int,
                  dtype: torch.dtype | None, device) -> None:
         self.need = need
+        self.every = need.every  # positions per row
         self.cache_layers = list(cache_layers)
         self.page_size = page_size
         self.allocator = PageAllocator(num_pages, page_size)
@@ -139,22 +143,27 @@ class CacheManager:
         self.device = torch.device(device) if device is not None else None
         by_need: dict[PagedKVNeed, list[int]] = {}
         state_needs: dict[int, SlotStateNeed] = {}
-        self.view_order: dict[int, tuple] = {}  # layers whose mixer keeps several things: the kinds, in its order
+        self.view_order: dict[int, tuple] = {}  # layers whose mixer keeps several things: its needs, in its order
         for layer in sorted(needs):
             several = isinstance(needs[layer], tuple)
-            kinds = []
+            seen = []
             for need in (needs[layer] if several else (needs[layer],)):
-                if isinstance(need, PagedKVNeed) and PagedKVNeed not in kinds:
+                if isinstance(need, PagedKVNeed) and need not in seen:
+                    if need.every < 1 or (need.every > 1 and (need.window is not None or need.block is not None)):
+                        raise ValueError(f"cache layer {layer}: rows per {need.every} positions cannot have a window")
                     by_need.setdefault(need, []).append(layer)
-                elif isinstance(need, SlotStateNeed) and SlotStateNeed not in kinds:
+                elif isinstance(need, SlotStateNeed) and not any(isinstance(n, SlotStateNeed) for n in seen):
                     state_needs[layer] = need
                 else:
-                    raise TypeError(f"cache layer {layer}: unknown need {need!r} (or two of a kind in one layer)")
-                kinds.append(type(need))
+                    raise TypeError(f"cache layer {layer}: unknown need {need!r} (or the same need twice in one layer)")
+                seen.append(need)
             if several:
-                self.view_order[layer] = tuple(kinds)
-        self.groups = [PageGroup(need, layers, num_pages, page_size, dtype, device) for need, layers in by_need.items()]
-        self.group_of_layer = {layer: g for g, group in enumerate(self.groups) for layer in group.cache_layers}
+                self.view_order[layer] = tuple(seen)
+        # a group of one row per `every` positions holds 1/every of the rows, and up to one part-filled page a request more
+        self.groups = [PageGroup(need, layers, num_pages if need.every == 1 else -(-num_pages // need.every) + num_state_slots,
+                                 page_size, dtype, device) for need, layers in by_need.items()]
+        self.group_of_need = {need: g for g, need in enumerate(by_need)}
+        self.group_of_layer = {layer: g for g, group in reversed(list(enumerate(self.groups))) for layer in group.cache_layers}
         self.state = StateSlots(state_needs, num_state_slots, device)
         self.watermark_pages = int(watermark * num_pages)  # clockwork/kvcache/block_manager.py:20
         self.requests: dict[str, RequestCache] = {}
@@ -188,8 +197,12 @@ class CacheManager:
         except KeyError:
             raise ValueError(f"request {request_id!r} holds no cache (double free?)") from None
 
-    def _blocks_for(self, num_tokens: int) -> int:
-        return (num_tokens + self.page_size - 1) // self.page_size
+    def _blocks_for(self, num_tokens: int, group: PageGroup | None = None) -> int:
+        """Pages that hold the rows of positions [0, num_tokens) (in a group of one row per ``every`` positions: the
+        rows of all blocks that these positions touch)."""
+        every = 1 if group is None else group.every
+        rows = (num_tokens + every - 1) // every
+        return (rows + self.page_size - 1) // self.page_size
 
     def pages_needed(self, req: RequestCache, new_len: int) -> list[int]:
         """Per group: pages to allocate so that positions [0, new_len) have slots, counting a
@@ -197,9 +210,9 @@ class CacheManager:
         need = []
         for g, group in enumerate(self.groups):
             table = req.tables[g]
-            n = max(0, self._blocks_for(new_len) - len(table))
+            n = max(0, self._blocks_for(new_len, group) - len(table))
             if new_len > req.num_tokens:
-                blk = req.num_tokens // self.page_size
+                blk = req.num_tokens // group.every // self.page_size
                 if blk < len(table) and table[blk] != NO_PAGE and group.allocator.is_shared(table[blk]):
                     n += 1
             need.append(n)
@@ -221,8 +234,8 @@ class CacheManager:
         the watermark left free."""
         if self.state.num_free == 0:
             return False
-        need = max(0, self._blocks_for(num_tokens) - shared_pages)
-        return all(g.allocator.num_free - need >= self.watermark_pages for g in self.groups)
+        return all(g.allocator.num_free - max(0, self._blocks_for(num_tokens, g) - shared_pages) >= self.watermark_pages
+                   for g in self.groups)
 
     def reserve(self, req: RequestCache, new_len: int) -> None:
         """Make sure positions [0, new_len) have slots in every group: allocate pages, and give
@@ -237,7 +250,7 @@ class CacheManager:
             raise OutOfPages(f"request {req.request_id!r}: not enough free pages to reach {new_len} tokens")
         for g, group in enumerate(self.groups):
             table = req.tables[g]
-            blk = req.num_tokens // self.page_size
+            blk = req.num_tokens // group.every // self.page_size
             if blk < len(table) and table[blk] != NO_PAGE:
                 cow = group.allocator.copy_on_write(table[blk])
                 if cow is not None:
@@ -247,13 +260,14 @@ class CacheManager:
                     req.table_epoch += 1
                     if g == 0 and blk < req.shared_prefix_pages:
                         req.shared_prefix_pages = blk  # no longer the prefix cache's page
-            missing = self._blocks_for(new_len) - len(table)
+            missing = self._blocks_for(new_len, group) - len(table)
             if missing > 0:
                 table.extend(group.allocator.allocate_many(missing))
         req.num_tokens = new_len
         # From the page that new_len - 1 falls into onwards, every page was allocated or copied for this
         # request just now or earlier, so nobody else holds it (until a fork, which resets this).
-        req.writable_len = min(len(t) for t in req.tables) * self.page_size if req.tables else new_len
+        req.writable_len = (min(len(t) * group.every for t, group in zip(req.tables, self.groups)) * self.page_size
+                            if req.tables else new_len)
 
     def _copy_page(self, group: PageGroup, src: int, dst: int) -> None:
         if group.kv is None:
@@ -334,35 +348,40 @@ class CacheManager:
     # ---- what a step needs --------------------------------------------------------------------
     def slots(self, req: RequestCache, group: int, start: int, end: int) -> list[int]:
         """clockwork/kvcache/block_manager.py:92-98."""
-        table, size = req.tables[group], self.page_size
-        if not 0 <= start <= end <= len(table) * size:
-            raise ValueError(f"token range [{start}, {end}) outside the covered range [0, {len(table) * size})")
+        table, size, every = req.tables[group], self.page_size, self.groups[group].every
+        if not 0 <= start <= end <= len(table) * size * every:
+            raise ValueError(f"token range [{start}, {end}) outside the covered range [0, {len(table) * size * every})")
         out = []
         for pos in range(start, end):
-            page = table[pos // size]
+            row = pos // every  # (a group of one row per `every` positions: the row of the position's block)
+            page = table[row // size]
             if page == NO_PAGE:
                 raise ValueError(f"position {pos} lies in a page that was already given back")
-            out.append(page * size + pos % size)
+            out.append(page * size + row % size)
         return out
 
     def views(self, block_tables: list[torch.Tensor], slots: list[torch.Tensor], state_slots: torch.Tensor | None,
               state_slots_host: list[int]) -> dict[int, PagedView | StateView]:
         """Per cache layer, what its mixer sees this step."""
         out: dict[int, PagedView | StateView] = {}
+
+        def paged(g: int, layer: int) -> PagedView:
+            k, v = self.groups[g].layer_kv(layer)
+            return PagedView(k, v, block_tables[g], slots[g], True)
+
+        def state(layer: int) -> StateView:
+            return StateView(self.state.tensors[layer], state_slots, list(state_slots_host))
+
         for g, group in enumerate(self.groups):
             for layer in group.cache_layers:
-                k, v = group.layer_kv(layer)
-                out[layer] = PagedView(k, v, block_tables[g], slots[g], True)
-        for layer, tensor in self.state.tensors.items():
-            view = StateView(tensor, state_slots, list(state_slots_host))
-            if layer in self.view_order:  # the mixer keeps pages as well: both views, in the order it named its needs
-                both = {PagedKVNeed: out.get(layer), SlotStateNeed: view}
-                out[layer] = tuple(both[kind] for kind in self.view_order[layer])
-            else:
-                out[layer] = view
-        for layer, kinds in self.view_order.items():
-            if not isinstance(out[layer], tuple):  # (a tuple of one need)
-                out[layer] = (out[layer],)
+                if layer not in self.view_order:
+                    out[layer] = paged(g, layer)
+        for layer in self.state.tensors:
+            if layer not in self.view_order:
+                out[layer] = state(layer)
+        for layer, needs in self.view_order.items():  # a mixer that keeps several things: its views in the order of its needs
+            out[layer] = tuple(paged(self.group_of_need[need], layer) if isinstance(need, PagedKVNeed) else state(layer)
+                               for need in needs)
         return out
 
     # ---- accounting -----------------------------------------------------------------------------

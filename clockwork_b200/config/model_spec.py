@@ -47,6 +47,7 @@ class LayerSpec:
     mixer_norm: PartSpec
     ffn_norm: PartSpec
     prefix: str  # checkpoint name prefix of the layer's tensors, e.g. "model.layers.3"
+    block_params: dict[str, Any] = field(default_factory=dict, hash=False)  # what the block arrangement itself needs (constants)
 
 
 @dataclass(frozen=True)
@@ -78,6 +79,8 @@ class ModelSpec:
     embedding_scale: float = 1.0  # the embedding rows are multiplied by this (the output head, if tied, is not)
     logit_softcap: float | None = None  # logits <- cap * tanh(logits / cap)
     absolute_positions: PartSpec | None = None  # a position part that adds a vector per position to the embedding
+    pair_embedding: PartSpec | None = None  # an embedding part that adds a row chosen by (previous token, token)
+    keeps_layer_outputs: bool = False  # blocks read what the input rows and every earlier layer run left (a plane each)
     raw: dict[str, Any] = field(default_factory=dict)  # the config.json it came from
 
     def validate(self) -> None:

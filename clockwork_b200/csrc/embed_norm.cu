@@ -408,6 +408,159 @@ extern "C" int cw_softcap(float* x, long long n, float cap, cudaStream_t stream)
     return cw_launch_ordered(softcap_kernel, dim3(blocks), dim3(256), 0, stream, x, n, cap);
 }
 
+// ---- a second table read by a hash of (previous token, token) -------------------------------------------
+// x[n] += table[row], row = (previous * mul_prev + token * mul_cur) mod buckets; a request's first token reads row
+// `buckets` (the table has buckets + 1 rows).  The token before a portion's first one is what the step before left in
+// the request's state (one int32 per request: state[slots[s] * stride]); keep_last_token_kernel, launched after this
+// one, leaves the portion's last token there.  Rows of no request (tok_seq < 0) are left alone.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pair_embed_add_kernel(float* __restrict__ x, const T* __restrict__ table, const int* __restrict__ ids,
+                      const int* __restrict__ positions, const int* __restrict__ tok_seq, const int* __restrict__ q_start,
+                      const int* __restrict__ state, long long stride, const long long* __restrict__ slots, int buckets,
+                      long long mul_prev, long long mul_cur, int W, int V, int* __restrict__ status) {
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int seq = tok_seq[n];
+    if (seq < 0) return;
+    const int tok = ids[n];
+    int prev = -1;
+    if (n > q_start[seq])
+        prev = ids[n - 1];
+    else if (positions[n] > 0)
+        prev = state[slots[seq] * stride];
+    if (tok < 0 || tok >= V || prev >= V) {
+        if (threadIdx.x == 0) cw_report(status, CW_ST_TOKEN_RANGE, n, tok);
+        return;
+    }
+    long long row = buckets;
+    if (prev >= 0) {
+        row = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+        if (row < 0) row += buckets;
+    }
+    const T* from = table + (size_t)row * W;
+    float* to = x + (size_t)n * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) to[c] += to_f(from[c]);
+}
+
+__global__ void __launch_bounds__(128)
+keep_last_token_kernel(const int* __restrict__ ids, const int* __restrict__ tok_seq, const int* __restrict__ q_start,
+                       int* __restrict__ state, long long stride, const long long* __restrict__ slots, int S) {
+    pdl_wait();
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= S) return;
+    const int a = q_start[s], b = q_start[s + 1];
+    if (b <= a || tok_seq[a] < 0) return;
+    state[slots[s] * stride] = ids[b - 1];
+}
+
+extern "C" int cw_pair_embed_add(float* x, const void* table, const int* ids, const int* positions, const int* tok_seq,
+                                 const int* q_start, int* state, long long stride, const long long* slots, int buckets,
+                                 long long mul_prev, long long mul_cur, int N, int S, int W, int V, int dtype, int* status,
+                                 cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || S <= 0 || W <= 0 || buckets <= 0 || stride <= 0) return CW_ERR_BAD_SIZE;
+    int threads = 64;
+    while (threads < 256 && threads * 4 < W) threads *= 2;
+    int rc;
+    if (dtype == 0)
+        rc = cw_launch_ordered(pair_embed_add_kernel<float>, dim3(N), dim3(threads), 0, stream, x, (const float*)table, ids, positions,
+                               tok_seq, q_start, (const int*)state, stride, slots, buckets, mul_prev, mul_cur, W, V, status);
+    else if (dtype == 1)
+        rc = cw_launch_ordered(pair_embed_add_kernel<bf16>, dim3(N), dim3(threads), 0, stream, x, (const bf16*)table, ids, positions,
+                               tok_seq, q_start, (const int*)state, stride, slots, buckets, mul_prev, mul_cur, W, V, status);
+    else
+        return CW_ERR_BAD_DTYPE;
+    if (rc != 0) return rc;
+    // (after the reader, in stream order: no block reads a token that another has just replaced)
+    return cw_launch_ordered(keep_last_token_kernel, dim3((S + 127) / 128), dim3(128), 0, stream, ids, tok_seq, q_start, state, stride,
+                             slots, S);
+}
+
+// ---- a scaled contribution into the residual, and the norm that reads it -----------------------------------
+// y = x + ca a (+ cb b) goes to `sum` (which may be x itself); out = y / sqrt(mean(y^2) + eps) * w.  Everything float32
+// but `out`.
+template <typename T>
+__global__ void __launch_bounds__(256)
+axpy_rmsnorm_kernel(const float* x, const float* __restrict__ a, const float* __restrict__ b, float ca, float cb,
+                    float* sum, const float* __restrict__ w, T* __restrict__ out, float eps, int W) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t at = (size_t)blockIdx.x * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float y = fmaf(ca, a[at + c], x[at + c]);
+        if (b != nullptr) y = fmaf(cb, b[at + c], y);
+        sum[at + c] = y;
+        ss = fmaf(y, y, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) out[at + c] = from_f<T>(sum[at + c] * inv * w[c]);  // (the thread's own writes)
+}
+
+extern "C" int cw_axpy_rmsnorm(const float* x, const float* a, const float* b, float ca, float cb, float* sum, const float* w,
+                               void* out, float eps, int N, int W, int dtype, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || W <= 0 || a == nullptr || x == nullptr || sum == nullptr) return CW_ERR_BAD_SIZE;
+    int threads = 64;
+    while (threads < 256 && threads * 4 < W) threads *= 2;
+    if (dtype == 0)
+        return cw_launch_ordered(axpy_rmsnorm_kernel<float>, dim3(N), dim3(threads), 0, stream, x, a, b, ca, cb, sum, w, (float*)out, eps, W);
+    if (dtype == 1)
+        return cw_launch_ordered(axpy_rmsnorm_kernel<bf16>, dim3(N), dim3(threads), 0, stream, x, a, b, ca, cb, sum, w, (bf16*)out, eps, W);
+    return CW_ERR_BAD_DTYPE;
+}
+
+// ---- the weighted average over the depth ------------------------------------------------------------------
+// history [runs + 1][N][W] holds what the input rows were (plane 0) and what every layer run left (plane r + 1).  This
+// kernel finishes run `index - 1`: y = x + ca a (+ cb b) (a may be null: y = x) goes to plane `index`, and what the next
+// layer reads is next = sum over j <= index of coef[j] * plane j, in the order of j.  x may be plane `index` itself, and
+// `next` may be x when x is no plane.  With a norm weight the rows of `next` are also normed into `normed`.
+template <typename T>
+__global__ void __launch_bounds__(256)
+depth_average_kernel(const float* x, const float* __restrict__ a, const float* __restrict__ b, float ca, float cb,
+                     float* history, long long plane, int index, const float* __restrict__ coef, float* next,
+                     const float* __restrict__ w, T* __restrict__ normed, float eps, int W) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    const size_t at = (size_t)blockIdx.x * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float y = x[at + c];
+        if (a != nullptr) y = fmaf(ca, a[at + c], y);
+        if (b != nullptr) y = fmaf(cb, b[at + c], y);
+        history[(size_t)index * plane + at + c] = y;
+        float acc = 0.f;
+        for (int j = 0; j < index; ++j) acc = fmaf(coef[j], history[(size_t)j * plane + at + c], acc);
+        acc = fmaf(coef[index], y, acc);
+        next[at + c] = acc;
+        ss = fmaf(acc, acc, ss);
+    }
+    if (w == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) normed[at + c] = from_f<T>(next[at + c] * inv * w[c]);
+}
+
+extern "C" int cw_depth_average(const float* x, const float* a, const float* b, float ca, float cb, float* history, long long plane,
+                                int index, const float* coef, float* next, const float* w, void* normed, float eps, int N, int W,
+                                int dtype, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || W <= 0 || index < 1 || plane < (long long)N * W || x == nullptr || history == nullptr || coef == nullptr || next == nullptr)
+        return CW_ERR_BAD_SIZE;
+    if (w != nullptr && normed == nullptr) return CW_ERR_BAD_SIZE;
+    int threads = 64;
+    while (threads < 256 && threads * 4 < W) threads *= 2;
+    if (dtype == 0)
+        return cw_launch_ordered(depth_average_kernel<float>, dim3(N), dim3(threads), 0, stream, x, a, b, ca, cb, history, plane, index, coef,
+                                 next, w, (float*)normed, eps, W);
+    if (dtype == 1)
+        return cw_launch_ordered(depth_average_kernel<bf16>, dim3(N), dim3(threads), 0, stream, x, a, b, ca, cb, history, plane, index, coef,
+                                 next, w, (bf16*)normed, eps, W);
+    return CW_ERR_BAD_DTYPE;
+}
+
 static int g_pdl = 1;
 extern "C" int cw_pdl_enabled() { return g_pdl; }
 extern "C" int cw_set_pdl(int on) { g_pdl = on ? 1 : 0; return CW_OK; }

@@ -384,12 +384,17 @@ extern "C" int cw_grouped_gemm(const void* A, int lda, int a_group_off, const vo
 // largest (the lower index wins a tie).  sel < 0 marks a padding row.  A warp per token.
 //   mode 0: weights = softmax over the chosen logits.
 //   mode 1: scores = softmax over all E logits; weights = the chosen experts' scores as they are.
-// groups > 1: the experts lie in `groups` equal runs of neighbours; a run counts as its largest entry, and
-// only experts of the `keep` best runs can be chosen.
+//   mode 2: scores = sigmoid of each logit; experts are ranked by score + correction[e] (`correction` null: by the score),
+//           weights = the chosen experts' scores without the correction.
+// Every weight is multiplied by weight_scale at the end.
+// groups > 1: the experts lie in `groups` equal runs of neighbours; a run counts as the sum of its `group_rank` largest
+// entries (1: its largest entry), and only experts of the `keep` best runs can be chosen (the others count as minus
+// infinity, whatever the sign of the entries).
 __global__ void __launch_bounds__(128)
 moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b, const int* __restrict__ tok_seq,
-                  int* __restrict__ sel, float* __restrict__ wt, int N, int E, int top, int mode, int groups, int keep) {
-    extern __shared__ float choose_s[];  // per warp: [E] logits or scores, [top] chosen ones, [groups] the runs' best
+                  int* __restrict__ sel, float* __restrict__ wt, int N, int E, int top, int mode, int groups, int keep,
+                  const float* __restrict__ correction, float weight_scale, int group_rank) {
+    extern __shared__ float choose_s[];  // per warp: [E] logits or scores, [top] chosen ones, [groups] the runs' best, [E] plain scores
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * 4 + warp;
@@ -401,9 +406,10 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b,
         }
         return;
     }
-    float* logit_s = choose_s + (size_t)warp * (E + top + groups);
+    float* logit_s = choose_s + (size_t)warp * (2 * E + top + groups);
     float* chosen_s = logit_s + E;
     float* group_s = chosen_s + top;
+    float* score_s = group_s + groups;  // mode 2: the scores that become weights
     for (int e = lane; e < E; e += 32) logit_s[e] = logits[(size_t)row * E + e] + (b != nullptr ? b[e] : 0.f);
     __syncwarp();
     if (mode == 1) {  // every expert's share of the softmax over all of them (sums in a fixed order)
@@ -416,12 +422,31 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b,
         for (int e = lane; e < E; e += 32) logit_s[e] = expf(logit_s[e] - mx) / sum;
         __syncwarp();
     }
+    if (mode == 2) {
+        for (int e = lane; e < E; e += 32) {
+            const float sc = 1.f / (1.f + expf(-logit_s[e]));
+            score_s[e] = sc;
+            logit_s[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+        }
+        __syncwarp();
+    }
     if (groups > 1) {
         const int per = E / groups;
         for (int g = lane; g < groups; g += 32) {
-            float best = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, logit_s[e]);
-            group_s[g] = best;
+            float rank = 0.f;
+            int taken[4] = {-1, -1, -1, -1};  // (group_rank <= 4)
+            for (int r = 0; r < group_rank; ++r) {  // the largest entries one by one, the lower index first among equals
+                float best = -INFINITY;
+                int at = -1;
+                for (int e = g * per; e < (g + 1) * per; ++e) {
+                    bool used = false;
+                    for (int u = 0; u < r; ++u) used = used || taken[u] == e;
+                    if (!used && (at < 0 || logit_s[e] > best)) best = logit_s[e], at = e;
+                }
+                taken[r] = at;
+                rank = r == 0 ? best : rank + best;
+            }
+            group_s[g] = rank;
         }
         __syncwarp();
         for (int t = 0; t < keep; ++t) {  // the best runs one by one; a kept run is marked with +inf
@@ -464,24 +489,33 @@ moe_choose_kernel(const float* __restrict__ logits, const float* __restrict__ b,
         __syncwarp();
     }
     if (mode == 1) {
-        for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = chosen_s[t] == -INFINITY ? 0.f : chosen_s[t];
+        for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = chosen_s[t] == -INFINITY ? 0.f : chosen_s[t] * weight_scale;
+        return;
+    }
+    if (mode == 2) {
+        for (int t = lane; t < top; t += 32) {
+            const int e = sel[(size_t)row * top + t];  // (written by lane 0 above, made visible by __syncwarp)
+            wt[(size_t)row * top + t] = chosen_s[t] == -INFINITY ? 0.f : score_s[e] * weight_scale;
+        }
         return;
     }
     const float first = chosen_s[0];
     float total = 0.f;
     for (int t = 0; t < top; ++t) total += expf(chosen_s[t] - first);  // the same order in every lane
-    for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = expf(chosen_s[t] - first) / total;
+    for (int t = lane; t < top; t += 32) wt[(size_t)row * top + t] = expf(chosen_s[t] - first) / total * weight_scale;
 }
 
 extern "C" int cw_moe_choose(const float* logits, const float* b, const int* tok_seq, int* sel, float* wt, int N, int E, int top,
-                             int mode, int groups, int keep, cudaStream_t stream) {
+                             int mode, int groups, int keep, const float* correction, float weight_scale, int group_rank,
+                             cudaStream_t stream) {
     if (N == 0) return CW_OK;
-    if (N < 0 || E <= 0 || top <= 0 || top > E || mode < 0 || mode > 1) return CW_ERR_BAD_SIZE;
+    if (N < 0 || E <= 0 || top <= 0 || top > E || mode < 0 || mode > 2) return CW_ERR_BAD_SIZE;
     if (groups < 1 || E % groups || keep < 1 || keep > groups || (long long)keep * (E / groups) < top) return CW_ERR_BAD_SIZE;
-    const size_t smem = 4 * (size_t)(E + top + groups) * sizeof(float);
+    if (group_rank < 1 || group_rank > 4 || group_rank > E / groups) return CW_ERR_BAD_SIZE;
+    const size_t smem = 4 * (size_t)(2 * E + top + groups) * sizeof(float);
     if (smem > (48 << 10)) return CW_ERR_UNSUPPORTED;
     return cw_launch_ordered(moe_choose_kernel, dim3((N + 3) / 4), dim3(128), smem, stream, logits, b, tok_seq, sel, wt, N, E, top,
-                             mode, groups, keep);
+                             mode, groups, keep, correction, weight_scale, group_rank);
 }
 
 // ---- pairs by expert --------------------------------------------------------------------------------

@@ -431,17 +431,49 @@ extern "C" int cw_sigmoid_power_decay(float* pre, int ldp, int N, int C, float i
     return cw_launch_ordered(sigmoid_power_decay_kernel, dim3(blocks), dim3(256), 0, stream, pre, ldp, N, C, inv_tau);
 }
 
+// ---- forget gates with a lower bound ---------------------------------------------------------------------
+// On rows [q (C) | z (C) | ..] of a product's float32 output: q <- silu(q);  f = lower + (1 - lower) sigmoid(z + bias) replaces
+// z (the decay of a channel of the state), and 1 - f goes to `take` [N, C] (what the channel takes of the new value).
+__global__ void __launch_bounds__(256)
+bounded_forget_kernel(float* __restrict__ x, int ld, const float* __restrict__ bias, const float* __restrict__ lower,
+                      float* __restrict__ take, int N, int C) {
+    pdl_wait();
+    const long long total = (long long)N * C;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / C), c = (int)(i - (long long)t * C);
+        float* row = x + (size_t)t * ld;
+        const float q = row[c];
+        row[c] = q / (1.f + expf(-q));
+        const float z = row[C + c] + (bias != nullptr ? bias[c] : 0.f);
+        const float l = lower[c];
+        const float f = fmaf(1.f - l, 1.f / (1.f + expf(-z)), l);
+        row[C + c] = f;
+        take[i] = 1.f - f;
+    }
+}
+
+extern "C" int cw_bounded_forget(float* x, int ld, const float* bias, const float* lower, float* take, int N, int C,
+                                 cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || C <= 0 || ld < 2 * C || lower == nullptr || take == nullptr) return CW_ERR_BAD_SIZE;
+    const long long total = (long long)N * C;
+    const int blocks = (int)min((long long)148 * 8, (total + 255) / 256);
+    return cw_launch_ordered(bounded_forget_kernel, dim3(blocks), dim3(256), 0, stream, x, ld, bias, lower, take, N, C);
+}
+
 // ---- gated norm in parts ----------------------------------------------------------------------------
 // y [N, C] float32, gate z [N, ldz] float32.  mode bit 0 (gate first): u = y gate(z), out = u / rms_part(u) * weight.
 // Otherwise: out = y / rms_part(y) * weight * gate(z).  mode bit 1: gate = sigmoid (else silu).  mode bit 2: every
-// part uses the same weight of one part's width.  A block per (row, part); sums in a fixed order.
+// part uses the same weight of one part's width.  mode bit 3: no gate at all (z may be null).  A block per (row, part);
+// sums in a fixed order.
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ weight,
                         T* __restrict__ out, int C, int parts, float eps, int mode) {
     __shared__ float scratch[33];
     pdl_wait();
-    const int gate_first = mode & 1;
+    const bool ungated = mode & 8;
+    const int gate_first = ungated ? 0 : (mode & 1);
     const bool plain_sigmoid = mode & 2;
     const int row = blockIdx.x, p = blockIdx.y;
     const int width = C / parts;
@@ -460,8 +492,8 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float g = zr[c];
-        const float sg = (plain_sigmoid ? 1.f : g) / (1.f + expf(-g));
+        const float g = ungated ? 0.f : zr[c];
+        const float sg = ungated ? 1.f : (plain_sigmoid ? 1.f : g) / (1.f + expf(-g));
         const float u = gate_first ? yr[c] * sg : yr[c];
         float r = u * inv * wr[c];
         if (!gate_first) r *= sg;
@@ -472,7 +504,8 @@ gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ z
 extern "C" int cw_gated_group_norm(const float* y, const float* z, int ldz, const float* weight, void* out, int N, int C,
                                    int parts, float eps, int mode, int dtype, cudaStream_t stream) {
     if (N == 0) return CW_OK;
-    if (N < 0 || C <= 0 || parts <= 0 || C % parts || ldz < C || parts > 65535) return CW_ERR_BAD_SIZE;
+    if (N < 0 || C <= 0 || parts <= 0 || C % parts || parts > 65535) return CW_ERR_BAD_SIZE;
+    if (!(mode & 8) && (z == nullptr || ldz < C)) return CW_ERR_BAD_SIZE;
     const int width = C / parts;
     int threads = 32;
     while (threads < 256 && threads * 4 < width) threads *= 2;

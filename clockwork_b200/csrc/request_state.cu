@@ -22,7 +22,9 @@ struct StepFromStateParams {
     int* fresh;           // [B] 1: take the row's column from `fresh_values` first (cleared here)
     const int* fresh_values;  // [CW_RS_FIELDS][B]
     int* state;           // [CW_RS_FIELDS][num_slots]
-    int num_slots, B, page_size, max_blocks, num_pages, num_groups;
+    int num_slots, B, page_size, max_blocks, num_groups;
+    int group_pages[CW_RS_MAX_GROUPS];  // per page group: pages of its pool
+    int group_every[CW_RS_MAX_GROUPS];  // per page group: positions per cache row (1: a row per position)
     const int* tables[CW_RS_MAX_GROUPS];  // per page group: [B][max_blocks] block tables of the rows
     int* kv_slots[CW_RS_MAX_GROUPS];      // per page group: [B] cache slot of each row's token (out)
     int* tokens;      // [B] out
@@ -82,10 +84,11 @@ __global__ void step_from_state_kernel(const StepFromStateParams p) {
     const unsigned long long seed = ((unsigned long long)(unsigned)col[CW_RS_SEED_HI * p.num_slots] << 32) |
                                     (unsigned)col[CW_RS_SEED_LO * p.num_slots];
     p.uniform[r] = uniform_for(seed, col[CW_RS_DRAWS * p.num_slots]);
-    const int blk = pos / p.page_size, off = pos - blk * p.page_size;
     for (int g = 0; g < p.num_groups; ++g) {
+        const int row = pos / p.group_every[g];  // (a group of one row per `every` positions: the row of the position's block)
+        const int blk = row / p.page_size, off = row - blk * p.page_size;
         const int page = (pos >= 0 && blk < p.max_blocks) ? p.tables[g][(size_t)r * p.max_blocks + blk] : -1;
-        if (page < 0 || page >= p.num_pages) {
+        if (page < 0 || page >= p.group_pages[g]) {
             cw_report(p.status, CW_ST_PAGE_RANGE, r, page);
             p.kv_slots[g][r] = -1;
         } else {
@@ -94,9 +97,11 @@ __global__ void step_from_state_kernel(const StepFromStateParams p) {
     }
 }
 
-// tables / kv_slots: `num_groups` device pointers each (host arrays of pointers).
+// tables / kv_slots: `num_groups` device pointers each (host arrays of pointers); group_pages / group_every: `num_groups`
+// host integers each (null: every group has `num_pages` pages / one row per position).
 extern "C" int cw_step_from_state(const int* row_slot, int* fresh, const int* fresh_values, int* state, int num_slots,
                                   int B, int page_size, int max_blocks, int num_pages, int num_groups,
+                                  const int* group_pages, const int* group_every,
                                   const int* const* tables, int* const* kv_slots, int* tokens, int* positions,
                                   int* ctx_lens, int* tok_seq, float* temperature, int* top_k, float* top_p,
                                   float* uniform, int* status, cudaStream_t stream) {
@@ -105,9 +110,12 @@ extern "C" int cw_step_from_state(const int* row_slot, int* fresh, const int* fr
         return CW_ERR_BAD_SIZE;
     StepFromStateParams p;
     p.row_slot = row_slot; p.fresh = fresh; p.fresh_values = fresh_values; p.state = state;
-    p.num_slots = num_slots; p.B = B; p.page_size = page_size; p.max_blocks = max_blocks; p.num_pages = num_pages;
+    p.num_slots = num_slots; p.B = B; p.page_size = page_size; p.max_blocks = max_blocks;
     p.num_groups = num_groups;
     for (int g = 0; g < CW_RS_MAX_GROUPS; ++g) {
+        p.group_pages[g] = g < num_groups && group_pages != nullptr ? group_pages[g] : num_pages;
+        p.group_every[g] = g < num_groups && group_every != nullptr ? group_every[g] : 1;
+        if (p.group_every[g] < 1) return CW_ERR_BAD_SIZE;
         p.tables[g] = g < num_groups ? tables[g] : nullptr;
         p.kv_slots[g] = g < num_groups ? kv_slots[g] : nullptr;
     }

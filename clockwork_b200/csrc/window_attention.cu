@@ -15,7 +15,15 @@
 //                        denominator once, with no key and no value)
 //   cw_rotate_store      turns the leading entries of every query and key head by the token's position (entry i with
 //                        entry i + dims/2), writes the queries out and the rows [key | value] into the cache
+//   cw_pool_rows         for every token that ends a block of `pool` positions: the mean of the block's rows [key | value]
+//                        as the cache holds them, into the row of a second cache that the token's slot there names
 //   (window_merge_kernel adds up the parts of a token's window; only launched when windows are cut)
+// Further switches of cw_window_attention (WindowExtras; each usable alone): a window that never closes (window >= 2^30:
+// plain causal attention); `pool`: beside the window, every block of `pool` positions that ends at or before p - window is
+// seen as one key and value, read from the second cache (its rows come first in a row's order of keys); `softcap`: the
+// score (after the numbers per head) becomes cap tanh(score / cap); `slopes`: slope[h] (p - j) is taken off the (capped)
+// score; a query temperature: the score is multiplied by 1 + coef ln(floor((p + 1) / every) + 1) first of all; `gate`: head
+// h's output is multiplied by sigmoid(gate[n, h]).
 // bfloat16 calls run the tensor-core form further down when it takes the sizes; the CUDA-core kernel is the float32
 // path and the fallback.
 //
@@ -119,6 +127,61 @@ extern "C" int cw_rotate_store(const float* src, int ld, const int* positions, c
     return CW_ERR_BAD_DTYPE;
 }
 
+// ---- the means of whole blocks of positions -----------------------------------------------------------------
+// A block per token.  A token at position p with (p + 1) % pool == 0 ends the block of positions p - pool + 1 .. p: the
+// mean of those positions' cache rows [G, dk + dv] (summed in float32 in the order of the positions, divided by pool, rounded
+// once) goes to row pool_slots[n] of the second cache.  The positions' rows are in the cache when the kernel runs: the
+// step's own tokens were stored before, and the cache manager keeps at least the last `pool` positions of a request.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pool_rows_kernel(const T* __restrict__ cache, const int* __restrict__ block_tables, int max_blocks, int page_size, int num_pages,
+                 const int* __restrict__ positions, const int* __restrict__ tok_seq, const int* __restrict__ pool_slots,
+                 T* __restrict__ pool_cache, long long pool_rows, int width, int pool, int* __restrict__ status) {
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int seq = tok_seq[n];
+    if (seq < 0) return;
+    const int p = positions[n];
+    if ((p + 1) % pool != 0) return;
+    const int slot = pool_slots[n];
+    if (slot < 0) return;
+    if (slot >= pool_rows) {
+        if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, n, slot);
+        return;
+    }
+    const int* table = block_tables + (size_t)seq * max_blocks;
+    const float inv = 1.0f / (float)pool;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float sum = 0.f;
+        for (int j = p - pool + 1; j <= p; ++j) {
+            const int blk = j / page_size;
+            const int page = blk < max_blocks ? table[blk] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (c == 0) cw_report(status, CW_ST_PAGE_RANGE, n, page);
+                continue;
+            }
+            sum += to_f(cache[((size_t)page * page_size + j % page_size) * width + c]);
+        }
+        pool_cache[(size_t)slot * width + c] = from_f<T>(sum * inv);
+    }
+}
+
+extern "C" int cw_pool_rows(const void* cache, const int* block_tables, int max_blocks, int page_size, int num_pages,
+                            const int* positions, const int* tok_seq, const int* pool_slots, void* pool_cache, long long pool_rows,
+                            int width, int pool, int N, int dtype, int* status, cudaStream_t stream) {
+    if (N == 0) return CW_OK;
+    if (N < 0 || width <= 0 || pool <= 0 || page_size <= 0 || max_blocks <= 0 || pool_rows <= 0) return CW_ERR_BAD_SIZE;
+    int threads = 32;
+    while (threads < 256 && threads < width) threads *= 2;
+    if (dtype == 0)
+        return cw_launch_ordered(pool_rows_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float*)cache, block_tables, max_blocks,
+                                 page_size, num_pages, positions, tok_seq, pool_slots, (float*)pool_cache, pool_rows, width, pool, status);
+    if (dtype == 1)
+        return cw_launch_ordered(pool_rows_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)cache, block_tables, max_blocks,
+                                 page_size, num_pages, positions, tok_seq, pool_slots, (bf16*)pool_cache, pool_rows, width, pool, status);
+    return CW_ERR_BAD_DTYPE;
+}
+
 struct WindowAttentionArgs {
     const void* q;            // [N, ldq]: head h's query at columns h*dk ..
     int ldq;
@@ -140,7 +203,27 @@ struct WindowAttentionArgs {
     int parts, part_keys;     // a token's window in `parts` pieces of `part_keys` keys (a multiple of tile)
     float* partial;           // parts > 1: [N, parts, H*dv + 2H] sums, running maxima and denominators
     int* status;
+    // further switches (all off when zero or null)
+    float softcap;            // > 0: score <- softcap tanh(score / softcap)
+    const float* slopes;      // [H] or null: slopes[h] * (p - j) is taken off the score
+    float temp_coef;          // with temp_every > 0: the score of a query at position p is multiplied by
+    int temp_every;           //   1 + temp_coef ln(floor((p + 1) / temp_every) + 1)
+    const float* gate;        // [N, ldg] or null: head h's output is multiplied by sigmoid(gate[n * ldg + h])
+    int ldg;
+    int pool;                 // > 0: blocks of `pool` positions that end at or before p - window are seen as one row each
+    const void* pool_cache;   // [rows, G, dk + dv]: row b of a request is the mean of its positions b*pool .. b*pool + pool - 1
+    const int* pool_tables;   // [S, pool_max_blocks]
+    int pool_max_blocks, pool_pages;
 };
+
+// how many pooled blocks position p sees: those that end at or before p - window
+__device__ __forceinline__ int wa_pooled_blocks(int p, int window, int pool) {
+    const int behind = p - window + 1;  // positions before the window
+    return pool > 0 && behind > 0 ? behind / pool : 0;
+}
+__device__ __forceinline__ float wa_query_temperature(int p, float coef, int every) {
+    return every > 0 ? 1.f + coef * logf((float)((p + 1) / every + 1)) : 1.f;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(1024)
@@ -160,8 +243,12 @@ window_attention_kernel(const WindowAttentionArgs a) {
     }
     const int p = a.positions[n];
     const int first = a.blocked ? p - p % a.window : max(0, p - a.window + 1);
-    const int lo = first + part * a.part_keys;
-    const int hi = min(p + 1, lo + a.part_keys);  // keys lo .. hi-1
+    // the row's keys in one order: its pooled blocks 0 .. nb-1, then the positions first .. p
+    const int nb = wa_pooled_blocks(p, a.window, a.pool);
+    const int lo = part * a.part_keys;
+    const int total = nb + p + 1 - first;
+    const int hi = part == a.parts - 1 ? total : min(total, lo + a.part_keys);  // keys lo .. hi-1 of that order (the last part: all the rest)
+    const float temperature = wa_query_temperature(p, a.temp_coef, a.temp_every);
     const int GK = G * dk, kstride = GK | 1;
     float* qs = wa_smem;               // [H*dk]
     float* Ks = qs + H * dk;           // [TK][kstride]
@@ -171,6 +258,7 @@ window_attention_kernel(const WindowAttentionArgs a) {
     float* lrun = mrun + H;            // [H] running denominator
     float* alpha = lrun + H;           // [H] what the sums so far are multiplied by when the maximum moves
     int* rows = (int*)(alpha + H);     // [TK] cache row of each key of the tile (-1: none)
+    int* dist = rows + TK;             // [TK] how far back the key lies (p - j); -1: a pooled block (its row is in the second cache)
     const T* q = (const T*)a.q + (size_t)n * a.ldq;
     for (int i = tid; i < H * dk; i += blockDim.x) qs[i] = to_f(q[i]);
     for (int h = tid; h < H; h += blockDim.x) {
@@ -182,29 +270,45 @@ window_attention_kernel(const WindowAttentionArgs a) {
 #pragma unroll
     for (int r = 0; r < WA_MAX_COLS; ++r) acc[r] = 0.f;
     const T* cache = (const T*)a.cache;
+    const T* pool_cache = (const T*)a.pool_cache;
     const int* table = a.block_tables + (size_t)seq * a.max_blocks;
+    const int* pool_table = a.pool > 0 ? a.pool_tables + (size_t)seq * a.pool_max_blocks : nullptr;
     const int warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
     for (int j0 = lo; j0 < hi; j0 += TK) {
         const int nk = min(TK, hi - j0);
         __syncthreads();  // the tile before is used up (and qs is written)
         if (tid < TK) {
-            int row = -1;
+            int row = -1, back = 0;
             if (tid < nk) {
-                const int pos = j0 + tid, blk = pos / a.page_size;
-                const int page = blk < a.max_blocks ? table[blk] : -1;
-                if (page < 0 || page >= a.num_pages)
-                    cw_report(a.status, CW_ST_PAGE_RANGE, n, page);
-                else
-                    row = page * a.page_size + pos % a.page_size;
+                const int v = j0 + tid;
+                if (v < nb) {  // a pooled block
+                    const int blk = v / a.page_size;
+                    const int page = blk < a.pool_max_blocks ? pool_table[blk] : -1;
+                    if (page < 0 || page >= a.pool_pages)
+                        cw_report(a.status, CW_ST_PAGE_RANGE, n, page);
+                    else
+                        row = page * a.page_size + v % a.page_size;
+                    back = -1;
+                } else {
+                    const int pos = first + (v - nb), blk = pos / a.page_size;
+                    const int page = blk < a.max_blocks ? table[blk] : -1;
+                    if (page < 0 || page >= a.num_pages)
+                        cw_report(a.status, CW_ST_PAGE_RANGE, n, page);
+                    else
+                        row = page * a.page_size + pos % a.page_size;
+                    back = p - pos;
+                }
             }
             rows[tid] = row;
+            dist[tid] = back;
         }
         __syncthreads();
         for (int idx = tid; idx < nk * GK; idx += blockDim.x) {
             const int j = idx / GK, c = idx - j * GK;
             const int g = c / dk, i = c - g * dk;
             const int row = rows[j];
-            Ks[j * kstride + c] = row >= 0 ? to_f(cache[((size_t)row * G + g) * row_width + i]) : 0.f;
+            const T* from = dist[j] < 0 ? pool_cache : cache;
+            Ks[j * kstride + c] = row >= 0 ? to_f(from[((size_t)row * G + g) * row_width + i]) : 0.f;
         }
         __syncthreads();
         for (int pair = tid; pair < H * TK; pair += blockDim.x) {  // key fastest: rows of Ks an odd stride apart
@@ -215,7 +319,7 @@ window_attention_kernel(const WindowAttentionArgs a) {
                 const float* qr = qs + h * dk;
                 for (int i = 0; i < dk; ++i) dot = fmaf(qr[i], kr[i], dot);
             }
-            sc[pair] = dot * a.scale;
+            sc[pair] = dot * a.scale * temperature;
         }
         __syncthreads();
         for (int h = warp; h < H; h += nwarps) {  // a warp per head, a lane per key of the tile
@@ -230,6 +334,8 @@ window_attention_kernel(const WindowAttentionArgs a) {
                 }
                 if (a.head_scale != nullptr) s *= a.head_scale[h];
                 if (a.head_bias != nullptr) s += a.head_bias[h];
+                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+                if (a.slopes != nullptr && dist[lane] > 0) s -= a.slopes[h] * (float)dist[lane];
             }
             if (a.sigmoid_weights) {
                 if (lane < TK) wt[h * TK + lane] = on ? 1.f / (1.f + expf(-s)) : 0.f;
@@ -253,12 +359,12 @@ window_attention_kernel(const WindowAttentionArgs a) {
             const int col = tid + r * blockDim.x;
             if (col < HV) {
                 const int h = col / dv, c = col - h * dv;
-                const T* vcol = cache + (size_t)(h / per) * row_width + dk + c;
+                const size_t voff = (size_t)(h / per) * row_width + dk + c;
                 const float* w = wt + h * TK;
                 float sum = a.sigmoid_weights ? acc[r] : acc[r] * alpha[h];
                 for (int j = 0; j < nk; ++j) {
                     const int row = rows[j];
-                    if (row >= 0) sum = fmaf(w[j], to_f(vcol[(size_t)row * G * row_width]), sum);
+                    if (row >= 0) sum = fmaf(w[j], to_f((dist[j] < 0 ? pool_cache : cache)[(size_t)row * G * row_width + voff]), sum);
                 }
                 acc[r] = sum;
             }
@@ -278,7 +384,9 @@ window_attention_kernel(const WindowAttentionArgs a) {
                 partial[col] = acc[r];
             } else {
                 const float l = a.sigmoid_weights ? 1.f : lrun[col / dv];
-                out[col] = from_f<T>(a.sigmoid_weights ? acc[r] : (l > 0.f ? acc[r] / l : 0.f));
+                float y = a.sigmoid_weights ? acc[r] : (l > 0.f ? acc[r] / l : 0.f);
+                if (a.gate != nullptr) y *= 1.f / (1.f + expf(-a.gate[(size_t)n * a.ldg + col / dv]));
+                out[col] = from_f<T>(y);
             }
         }
     }
@@ -294,7 +402,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ positions, const int* __restrict__ tok_seq,
                     int H, int dv, int window, int parts, int part_keys, int sigmoid_weights, int all_parts, int blocked,
-                    const float* __restrict__ sink, T* __restrict__ out) {
+                    const float* __restrict__ sink, T* __restrict__ out, int pool, const float* __restrict__ gate, int ldg) {
     __shared__ float factor[64];
     __shared__ float denominator;
     pdl_wait();
@@ -302,8 +410,8 @@ window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ p
     if (tok_seq[n] < 0) return;  // (the attention kernel wrote the zeros)
     const int HV = H * dv, stride = HV + 2 * H;
     const int p = positions[n];
-    const int keys = blocked ? p % window + 1 : p + 1 - max(0, p - window + 1);
-    const int used = all_parts ? parts : (keys + part_keys - 1) / part_keys;  // (parts that hold none of the row's keys add nothing)
+    const int keys = (blocked ? p % window + 1 : p + 1 - max(0, p - window + 1)) + wa_pooled_blocks(p, window, pool);
+    const int used = all_parts ? parts : min(parts, (keys + part_keys - 1) / part_keys);  // (parts that hold none of the row's keys add nothing)
     const float* base = partial + (size_t)n * parts * stride;
     if (threadIdx.x == 0) {
         float m = -INFINITY, l = 0.f;
@@ -320,11 +428,12 @@ window_merge_kernel(const float* __restrict__ partial, const int* __restrict__ p
     }
     __syncthreads();
     const float l = denominator;
+    const float open = gate != nullptr ? 1.f / (1.f + expf(-gate[(size_t)n * ldg + h])) : 1.f;
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         const int col = h * dv + c;
         float sum = 0.f;
         for (int s = 0; s < used; ++s) sum = fmaf(factor[s], base[(size_t)s * stride + col], sum);
-        out[(size_t)n * HV + col] = from_f<T>(l > 0.f ? sum / l : 0.f);
+        out[(size_t)n * HV + col] = from_f<T>((l > 0.f ? sum / l : 0.f) * open);
     }
 }
 
@@ -422,10 +531,15 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     const int gl = warp / per;      // its key/value head among the block's
     const int p0 = a.positions[row0];
     const int first = a.blocked ? p0 - p0 % a.window : max(0, p0 - a.window + 1);
-    // the keys that the tile's rows see, first .. p0 + rows - 1, in `parts` equal pieces of whole key tiles
-    const int part_keys = a.parts > 1 ? ((p0 + rows - first + a.parts - 1) / a.parts + WM_BN - 1) / WM_BN * WM_BN : p0 + rows - first;
-    const int lo = first + part * part_keys;
-    const int hi = min(p0 + rows, lo + part_keys);  // keys lo .. hi-1
+    // What the tile's rows see, in key tiles of 32: the pooled blocks 0 .. NB-1 that its last row sees (tiles 0 .. pool_tiles-1,
+    // the last of them part empty), then the positions first .. p0 + rows - 1; `parts` equal runs of whole key tiles.
+    const int NB = wa_pooled_blocks(p0 + rows - 1, a.window, a.pool);
+    const int pool_tiles = (NB + WM_BN - 1) / WM_BN;
+    const int all_tiles = pool_tiles + (p0 + rows - first + WM_BN - 1) / WM_BN;
+    const int part_tiles = (all_tiles + a.parts - 1) / a.parts;
+    const int t_lo = part * part_tiles;
+    const int t_hi = min(all_tiles, t_lo + part_tiles);  // key tiles t_lo .. t_hi-1
+    const int hi = p0 + rows;                            // positions below hi
     // shared memory: Q [nwarps][16][dk+8], then per stage K [GC][32][dk+8] and V [GC][32][dv+8] (bfloat16), then with
     // talk the scores of all heads [H][16][40] and the mixing matrix [H][H] (float32)
     const int qs = dk + 8, ks_ = dk + 8, vs_ = dv + 8;
@@ -445,7 +559,9 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     if (talk)
         for (int i = tid; i < H * H; i += blockDim.x) Tm[i] = a.talk[i];
     const bf16* cache = (const bf16*)a.cache;
+    const bf16* pool_cache = (const bf16*)a.pool_cache;
     const int* table = a.block_tables + (size_t)seq * a.max_blocks;
+    const int* pool_table = a.pool > 0 ? a.pool_tables + (size_t)seq * a.pool_max_blocks : nullptr;
     // A thread copies the same 16-byte piece (key/value head g, piece c of the row) of every `kstep`-th key of a tile, so
     // that what does not change from tile to tile is worked out once; pages are found by a shift when their size is a
     // power of two.
@@ -469,26 +585,44 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
         }
         return page;
     };
-    auto copy_piece = [&](int j, int g, int c, int pos, int stage) {
+    auto pool_page_of = [&](int b, int& offset) {  // pooled block b of the request: its page in the second cache
+        const int blk = b / a.page_size;
+        offset = b - blk * a.page_size;
+        int page = blk < a.pool_max_blocks ? pool_table[blk] : -1;
+        if (page < 0 || page >= a.pool_pages) {
+            cw_report(a.status, CW_ST_PAGE_RANGE, row0, page);
+            page = -1;
+        }
+        return page;
+    };
+    auto copy_piece = [&](int j, int g, int c, int t, int stage) {  // key j of key tile t
         bf16* Kst = KV + (size_t)stage * stage_elems;
         bf16* Vst = Kst + (size_t)GC * WM_BN * ks_;
         bf16* dst = c < kchunks ? Kst + ((size_t)g * WM_BN + j) * ks_ + c * 8 : Vst + ((size_t)g * WM_BN + j) * vs_ + (c - kchunks) * 8;
-        int offset = 0;
-        const int page = pos < hi ? page_of(pos, offset) : -1;
+        int offset = 0, page = -1;
+        const bf16* from = cache;
+        if (t < pool_tiles) {
+            const int b = t * WM_BN + j;
+            if (b < NB) page = pool_page_of(b, offset);
+            from = pool_cache;
+        } else {
+            const int pos = first + (t - pool_tiles) * WM_BN + j;
+            if (pos < hi) page = page_of(pos, offset);
+        }
         if (page >= 0)
-            wm_cp16(dst, cache + (((size_t)page * a.page_size + offset) * G + g0 + g) * row_width + c * 8);
+            wm_cp16(dst, from + (((size_t)page * a.page_size + offset) * G + g0 + g) * row_width + c * 8);
         else
             *(uint4*)dst = make_uint4(0, 0, 0, 0);
     };
     const int my_piece = tid % pieces, my_g = my_piece / chunks_per_row, my_c = my_piece - my_g * chunks_per_row;
-    auto fetch = [&](int j0, int stage) {  // keys j0 .. j0+31 of the block's key/value heads
+    auto fetch = [&](int t, int stage) {  // the 32 keys of key tile t, of the block's key/value heads
         if (strided && blockDim.x >= pieces) {
-            for (int j = tid / pieces; j < WM_BN; j += blockDim.x / pieces) copy_piece(j, my_g, my_c, j0 + j, stage);
+            for (int j = tid / pieces; j < WM_BN; j += blockDim.x / pieces) copy_piece(j, my_g, my_c, t, stage);
         } else {
             for (int idx = tid; idx < WM_BN * pieces; idx += blockDim.x) {
                 const int j = idx / pieces, piece = idx - j * pieces;
                 const int g = piece / chunks_per_row;
-                copy_piece(j, g, piece - g * chunks_per_row, j0 + j, stage);
+                copy_piece(j, g, piece - g * chunks_per_row, t, stage);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -499,25 +633,34 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int r_lo = lane >> 2, cpair = (lane & 3) * 2;  // this thread's rows r_lo and r_lo + 8, columns cpair, cpair + 1 of a tile of 8
     int row_first[2];  // the first position that each of the thread's two rows sees
+    int row_blocks[2];  // how many pooled blocks it sees
+    float row_temp[2];  // what its scores are multiplied by (a query temperature)
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         const int p = p0 + r_lo + 8 * x;
         row_first[x] = a.blocked ? p - p % a.window : p - a.window + 1;
+        row_blocks[x] = wa_pooled_blocks(p, a.window, a.pool);
+        row_temp[x] = wa_query_temperature(p, a.temp_coef, a.temp_every);
     }
+    const bool bent = a.softcap > 0.f || a.slopes != nullptr || a.temp_every > 0;  // scores that are more than scaled and shifted
+    const float slope = a.slopes != nullptr ? a.slopes[h] : 0.f;
+    const int first_blocks = wa_pooled_blocks(p0, a.window, a.pool);  // pooled blocks that every row of the tile sees
     const int last_first = a.blocked ? (p0 + 15) - (p0 + 15) % a.window : p0 + 15 - a.window + 1;  // of the tile's last row
     const float head_scale = a.head_scale != nullptr ? a.head_scale[h] : 1.f;
     const float head_bias = a.head_bias != nullptr ? a.head_bias[h] : 0.f;
     const int nvt = dv / 8, nks = dk / 16;
-    const int ntiles = hi > lo ? (hi - lo + WM_BN - 1) / WM_BN : 0;
-    if (ntiles > 0) fetch(lo, 0);
+    const int ntiles = t_hi > t_lo ? t_hi - t_lo : 0;
+    if (ntiles > 0) fetch(t_lo, 0);
     for (int t = 0; t < ntiles; ++t) {
-        const int j0 = lo + t * WM_BN;
+        const int kt = t_lo + t;              // the key tile
+        const bool pooled = kt < pool_tiles;  // its keys are pooled blocks kt*32 .., else positions j0 ..
+        const int j0 = pooled ? kt * WM_BN : first + (kt - pool_tiles) * WM_BN;
         const int stage = args.stages == 2 ? (t & 1) : 0;
         if (args.stages == 2 && t + 1 < ntiles) {
-            fetch(j0 + WM_BN, stage ^ 1);
+            fetch(kt + 1, stage ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
-            if (args.stages == 1 && t > 0) fetch(j0, 0);  // one stage: everyone left it at the end of the last round
+            if (args.stages == 1 && t > 0) fetch(kt, 0);  // one stage: everyone left it at the end of the last round
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();  // the tile has landed (and Q, at the first)
@@ -567,18 +710,27 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
         float tile_max[2] = {-INFINITY, -INFINITY};
         // (a tile that every row sees whole needs no mask: its last key is not behind the first row, its first not
         // before the last row's window)
-        const bool whole = rows == 16 && j0 + WM_BN - 1 <= p0 && j0 >= last_first && j0 + WM_BN <= hi;
+        const bool whole = pooled ? rows == 16 && j0 + WM_BN <= first_blocks
+                                  : rows == 16 && j0 + WM_BN - 1 <= p0 && j0 >= last_first && j0 + WM_BN <= hi;
 #pragma unroll
         for (int nt = 0; nt < WM_BN / 8; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 bool on = true;
+                const int j = j0 + nt * 8 + cpair + (e & 1);
                 if (!whole) {
-                    const int row = r_lo + (e >> 1) * 8, j = j0 + nt * 8 + cpair + (e & 1);
+                    const int row = r_lo + (e >> 1) * 8;
                     const int p = p0 + row;
-                    on = row < rows && j <= p && j >= row_first[e >> 1] && j < hi;
+                    on = pooled ? row < rows && j < row_blocks[e >> 1] : row < rows && j <= p && j >= row_first[e >> 1] && j < hi;
                 }
-                const float v = on ? fmaf(s[nt][e], head_scale, head_bias) : -INFINITY;
+                float v = s[nt][e];
+                if (bent) v *= row_temp[e >> 1];
+                v = fmaf(v, head_scale, head_bias);
+                if (bent) {
+                    if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                    if (!pooled) v -= slope * (float)(p0 + r_lo + (e >> 1) * 8 - j);
+                }
+                v = on ? v : -INFINITY;
                 s[nt][e] = v;
                 tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
             }
@@ -668,7 +820,8 @@ window_attention_mma_kernel(const WindowMmaArgs args) {
                 pr[HV + H + h] = l_run[x];
             }
         } else {
-            const float inv = a.sigmoid_weights ? 1.f : (l_run[x] > 0.f ? 1.f / l_run[x] : 0.f);
+            float inv = a.sigmoid_weights ? 1.f : (l_run[x] > 0.f ? 1.f / l_run[x] : 0.f);
+            if (a.gate != nullptr) inv *= 1.f / (1.f + __expf(-a.gate[n * a.ldg + h]));
 #pragma unroll
             for (int nt = 0; nt < DVMAX / 8; ++nt)
                 if (nt < nvt)
@@ -730,8 +883,13 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
                                    int G, int dk, int dv, int window, float scale, const float* head_scale,
                                    const float* talk, const float* head_bias, int sigmoid_weights, int blocked, const float* sink,
                                    void* out, int parts, float* partial, const int* q_start, int S, int dtype, int* status,
+                                   float softcap, const float* slopes, float temp_coef, int temp_every, const float* gate, int ldg,
+                                   int pool, const void* pool_cache, const int* pool_tables, int pool_max_blocks, int pool_pages,
                                    cudaStream_t stream) {
     if (N == 0) return CW_OK;
+    if (softcap < 0.f || temp_every < 0 || pool < 0 || (gate != nullptr && ldg < H)) return CW_ERR_BAD_SIZE;
+    if (pool > 0 && (pool_cache == nullptr || pool_tables == nullptr || pool_max_blocks <= 0 || pool_pages <= 0 || blocked || slopes != nullptr))
+        return CW_ERR_BAD_SIZE;  // (a pooled block has no distance, and blocks of positions have nothing before them)
     if (N < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || window <= 0 || page_size <= 0 || max_blocks <= 0 ||
         ldq < H * dk || parts < 1)
         return CW_ERR_BAD_SIZE;
@@ -743,14 +901,15 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     if (dtype == 1) {  // bfloat16: the tensor-core form when it takes the sizes
         const WindowAttentionArgs base = {q, ldq, cache, block_tables, max_blocks, page_size, num_pages, positions, tok_seq, H, G, dk, dv,
                                           window, scale, head_scale, talk, head_bias, sigmoid_weights, blocked, sink, out, WM_BN, parts, 0,
-                                          partial, status};
+                                          partial, status, softcap, slopes, temp_coef, temp_every, gate, ldg, pool, pool_cache, pool_tables,
+                                          pool_max_blocks, pool_pages};
         int launched = 0;
         const int rc = window_attention_mma(base, q_start, S, N, stream, &launched);
         if (rc != 0) return rc;
         if (launched) {
             if (parts == 1) return CW_OK;
             return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq, H,
-                                     dv, window, parts, 0, sigmoid_weights, 1, blocked, sink, (bf16*)out);
+                                     dv, window, parts, 0, sigmoid_weights, 1, blocked, sink, (bf16*)out, pool, gate, ldg);
         }
     }
     int threads = 128;
@@ -762,13 +921,17 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     int tile = 32;
     while (tile > 4 && (size_t)tile * kstride * sizeof(float) > (64u << 10)) tile >>= 1;
     const size_t smem = sizeof(float) * ((size_t)H * dk + (size_t)tile * kstride + 2 * (size_t)H * tile + 3 * (size_t)H) +
-                        sizeof(int) * tile;
+                        sizeof(int) * 2 * tile;
     if (smem > (200u << 10)) return CW_ERR_UNSUPPORTED;
-    int part_keys = (window + parts - 1) / parts;
+    // (a row's order of keys is cut in `parts` runs: float32 runs never cut, so the longest row that a cut must cover is a
+    // window and the pooled blocks before it; a window that never closes is cut as if it held 2^20 keys)
+    const long long longest = (long long)min(window, 1 << 20) + (pool > 0 ? (1 << 20) / pool : 0);
+    int part_keys = (int)((longest + parts - 1) / parts);
     part_keys = (part_keys + tile - 1) / tile * tile;
     WindowAttentionArgs a = {q, ldq, cache, block_tables, max_blocks, page_size, num_pages, positions, tok_seq, H, G, dk, dv,
                              window, scale, head_scale, talk, head_bias, sigmoid_weights, blocked, sink, out, tile, parts, part_keys,
-                             partial, status};
+                             partial, status, softcap, slopes, temp_coef, temp_every, gate, ldg, pool, pool_cache, pool_tables,
+                             pool_max_blocks, pool_pages};
     static size_t allowed[2] = {48 << 10, 48 << 10};
     if (dtype != 0 && dtype != 1) return CW_ERR_BAD_DTYPE;
     if (smem > allowed[dtype]) {
@@ -784,9 +947,9 @@ extern "C" int cw_window_attention(const void* q, int ldq, const void* cache, co
     if (rc != 0 || parts == 1) return rc;
     if (dtype == 0)
         return cw_launch_ordered(window_merge_kernel<float>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq,
-                                 H, dv, window, parts, part_keys, sigmoid_weights, 0, blocked, sink, (float*)out);
+                                 H, dv, window, parts, part_keys, sigmoid_weights, 0, blocked, sink, (float*)out, pool, gate, ldg);
     return cw_launch_ordered(window_merge_kernel<bf16>, dim3(N, H), dim3(merge_threads), 0, stream, (const float*)partial, positions, tok_seq, H,
-                             dv, window, parts, part_keys, sigmoid_weights, 0, blocked, sink, (bf16*)out);
+                             dv, window, parts, part_keys, sigmoid_weights, 0, blocked, sink, (bf16*)out, pool, gate, ldg);
 }
 
 CW_TRACE_TU(window_attention)

@@ -130,7 +130,8 @@ class StepBuilder:
             for i, r in enumerate(reqs):
                 table = np.asarray(r.tables[g], dtype=np.int32)
                 tables[i, : len(table)] = table
-                pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32)
+                # (a group of one row per `every` positions: the row of the position's block)
+                pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32) // cache.groups[g].every
                 pages = table[pos // ps]
                 if (pages == NO_PAGE).any():
                     raise RuntimeError(f"request {r.request_id!r}: a token lands in a page that was given back")
@@ -261,9 +262,9 @@ class DecodeGraph:
                 row_slot = view("row_slot")
                 state_rows.copy_(torch.where(row_slot < 0, cache.state.scratch_slot, row_slot))
             ops.step_from_state(view("row_slot"), view("fresh"), view("fresh_values").view(F, batch), state, tables, kv_slots,
-                                cache.page_size, cache.num_pages, view("tokens"), view("positions"), view("ctx_lens"),
+                                cache.page_size, [group.allocator.num_pages for group in cache.groups], view("tokens"), view("positions"), view("ctx_lens"),
                                 view("tok_seq"), as_float("temperature"), view("top_k"), as_float("top_p"),
-                                as_float("uniform"), runner.status)
+                                as_float("uniform"), runner.status, every=[group.every for group in cache.groups])
             # the logits of every row stay readable after a replay (trace replay reads them; generation
             # reads the sampled tokens only)
             logits = self.logits = model.forward(ctx, view("tokens"), view("rows"))
@@ -322,7 +323,7 @@ class DecodeGraph:
                 tables[i, have:held] = table[have:held]
                 owners[i] = (r, held, r.table_epoch)
                 dirty = True
-            pages = tables[rows, pos // ps]
+            pages = tables[rows, pos // cache.groups[g].every // ps]
             if (pages == NO_PAGE).any():
                 bad = reqs[int(np.argmax(pages == NO_PAGE))]
                 raise RuntimeError(f"request {bad.request_id!r}: a token lands in a page that was given back")
@@ -474,7 +475,7 @@ class PortionGraph:
                 # whole prompt's at admission; the step reads the table up to its context bound only)
                 held = min(len(table), self.max_blocks)
                 tables[i, :held] = table[:held]
-                pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32)
+                pos = np.arange(starts[i], ctx_lens[i], dtype=np.int32) // cache.groups[g].every
                 pages = table[pos // ps]
                 if (pages == NO_PAGE).any():
                     raise RuntimeError(f"request {r.request_id!r}: a token lands in a page that was given back")

@@ -93,14 +93,21 @@ def raise_on_status(status: torch.Tensor) -> None:
         raise RuntimeError("kernel status: " + STATUS_MESSAGES.get(code, f"code {code}").format(a=a, b=b))
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: bool = False, scale: float = 1.0) -> torch.Tensor:
+def embed(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, serial: bool = False, scale: float = 1.0,
+          out: torch.Tensor | None = None) -> torch.Tensor:
     """float32 [N, H] rows of ``table`` (float32 or bfloat16 [V, H]) for int32 ``ids`` [N], times ``scale``.  ``serial``: the
     kernel starts only when everything before it on the stream has finished (for a step whose inputs a
-    kernel has just written: the step's later kernels read them before they wait for anything)."""
+    kernel has just written: the step's later kernels read them before they wait for anything).  ``out``: where the
+    rows go (a contiguous float32 [N, H]) instead of a new tensor."""
     _need(table, None, "table", 2)
     _need(ids, torch.int32, "ids", 1)
     n, (v, h) = ids.shape[0], table.shape
-    out = torch.empty((n, h), dtype=torch.float32, device=table.device)
+    if out is None:
+        out = torch.empty((n, h), dtype=torch.float32, device=table.device)
+    else:
+        _need(out, torch.float32, "out", 2)
+        if tuple(out.shape) != (n, h):
+            raise ValueError(f"out {tuple(out.shape)} is not [{n}, {h}]")
 
     def launch():
         check(library().cw_embed(_ptr(out), _ptr(table), _ptr(ids), n, h, v, dtype_code(table.dtype), float(scale), _ptr(status), _stream()), "embed")
@@ -158,6 +165,80 @@ def sum_rmsnorm_add(resid: torch.Tensor, terms, weight: torch.Tensor, eps: float
     (a, ca), (b, cb) = terms[0], (terms[1] if len(terms) == 2 else (None, 0.0))
     check(library().cw_sum_rmsnorm_add(_ptr(resid), _ptr(a), _ptr(b), float(ca), float(cb), _ptr(weight), float(eps), n, w, _stream()),
           "sum_rmsnorm_add")
+
+
+def pair_embed_add(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, ctx, view, mul_prev: int, mul_cur: int) -> None:
+    """In place on float32 ``x`` [N, W]: row ``(previous token * mul_prev + token * mul_cur) mod buckets`` of ``table``
+    [buckets + 1, W] is added to every token's row; a request's first token (position 0) reads the last row.  The token
+    before a portion's first one comes from the request's state (``view``: int32 [slots, 1]), where the portion's last
+    token is left for the next step."""
+    _need(x, torch.float32, "x", 2)
+    _need(table, None, "table", 2)
+    _need(ids, torch.int32, "ids", 1)
+    _need(view.state, torch.int32, "state", 2)
+    _need(view.slots, torch.int64, "state slots", 1)
+    n, w = x.shape
+    if table.shape[1] != w or table.shape[0] < 2:
+        raise ValueError(f"table {tuple(table.shape)} does not fit rows of {w}")
+    check(library().cw_pair_embed_add(_ptr(x), _ptr(table), _ptr(ids), _ptr(ctx.positions), _ptr(ctx.tok_seq), _ptr(ctx.q_start),
+                                      _ptr(view.state), view.state.stride(0), _ptr(view.slots), table.shape[0] - 1, int(mul_prev),
+                                      int(mul_cur), n, ctx.num_seqs, w, 1 << 30, dtype_code(table.dtype), _ptr(ctx.status), _stream()),
+          "pair_embed_add")
+
+
+def axpy_rmsnorm(x: torch.Tensor, terms, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                 into: torch.Tensor | None = None) -> torch.Tensor:
+    """``y = x + sum of factor * tensor over the terms`` (one or two pairs (float32 [N, W], factor)) is written to ``into``
+    (``x`` itself when None); returns ``weight * rmsnorm(y)`` as ``out_dtype``.  Sums and statistics are float32."""
+    _need(x, torch.float32, "x", 2)
+    _need(weight, torch.float32, "weight", 1)
+    n, w = x.shape
+    if not 1 <= len(terms) <= 2:
+        raise ValueError("one or two terms")
+    for t, _ in terms:
+        _need(t, torch.float32, "term", 2)
+        if t.shape != x.shape:
+            raise ValueError(f"term {tuple(t.shape)} does not match the rows {tuple(x.shape)}")
+    into = x if into is None else into
+    _need(into, torch.float32, "into", 2)
+    if into.shape != x.shape or weight.shape[0] != w:
+        raise ValueError("into must have the rows' shape and weight their width")
+    (a, ca), (b, cb) = terms[0], (terms[1] if len(terms) == 2 else (None, 0.0))
+    out = torch.empty((n, w), dtype=out_dtype, device=x.device)
+    check(library().cw_axpy_rmsnorm(_ptr(x), _ptr(a), _ptr(b), float(ca), float(cb), _ptr(into), _ptr(weight), _ptr(out), float(eps), n, w,
+                                    dtype_code(out_dtype), _stream()), "axpy_rmsnorm")
+    return out
+
+
+def depth_average(x: torch.Tensor, terms, history: torch.Tensor, index: int, coef: torch.Tensor, into: torch.Tensor,
+                  norm_weight: torch.Tensor | None = None, eps: float = 0.0, out_dtype: torch.dtype | None = None):
+    """Ends a layer run: ``y = x + sum of factor * tensor over the terms`` (none, one or two pairs) becomes plane ``index``
+    of ``history`` [planes, N, W], and ``into`` receives ``sum over j <= index of coef[j] * history[j]`` (taken in the order
+    of j).  ``x`` may be plane ``index`` itself; ``into`` may be ``x`` when ``x`` is no plane.  With ``norm_weight`` also
+    returns ``norm_weight * rmsnorm(into)`` as ``out_dtype`` (else None).  All float32."""
+    _need(x, torch.float32, "x", 2)
+    _need(history, torch.float32, "history", 3)
+    _need(coef, torch.float32, "coef", 1)
+    _need(into, torch.float32, "into", 2)
+    n, w = x.shape
+    if tuple(history.shape[1:]) != (n, w) or not 1 <= index < history.shape[0] or coef.shape[0] != index + 1 or into.shape != x.shape:
+        raise ValueError(f"history {tuple(history.shape)}, plane {index}, {coef.shape[0]} coefficients do not fit rows {tuple(x.shape)}")
+    if len(terms) > 2:
+        raise ValueError("at most two terms")
+    for t, _ in terms:
+        _need(t, torch.float32, "term", 2)
+        if t.shape != x.shape:
+            raise ValueError(f"term {tuple(t.shape)} does not match the rows {tuple(x.shape)}")
+    pairs = list(terms) + [(None, 0.0)] * (2 - len(terms))
+    (a, ca), (b, cb) = pairs
+    normed = None
+    if norm_weight is not None:
+        _need(norm_weight, torch.float32, "norm_weight", 1)
+        normed = torch.empty((n, w), dtype=out_dtype, device=x.device)
+    check(library().cw_depth_average(_ptr(x), _ptr(a), _ptr(b), float(ca), float(cb), _ptr(history), history.stride(0), int(index),
+                                     _ptr(coef), _ptr(into), _ptr(norm_weight), _ptr(normed), float(eps), n, w,
+                                     dtype_code(out_dtype) if normed is not None else 0, _stream()), "depth_average")
+    return normed
 
 
 def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
@@ -393,15 +474,16 @@ def argmax(logits: torch.Tensor, out: torch.Tensor | None = None, into_state=Non
 
 
 def step_from_state(row_slot: torch.Tensor, fresh: torch.Tensor, fresh_values: torch.Tensor, state: torch.Tensor,
-                    tables: list[torch.Tensor], kv_slots: list[torch.Tensor], page_size: int, num_pages: int,
+                    tables: list[torch.Tensor], kv_slots: list[torch.Tensor], page_size: int, num_pages,
                     tokens: torch.Tensor, positions: torch.Tensor, ctx_lens: torch.Tensor, tok_seq: torch.Tensor,
                     temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
-                    status: torch.Tensor) -> None:
+                    status: torch.Tensor, every=None) -> None:
     """The inputs of a single-token step from the per-request state table: row r of the step belongs to
     the request in slot ``row_slot[r]`` (< 0: padding).  Rows flagged in ``fresh`` first take their column
     from ``fresh_values`` [fields, B] (the flag is cleared).  Written: the token to feed, position,
     context length, the row's request index, the cache slot per page group (from ``tables`` [B, max_blocks]
-    each), and the sampling parameters with the draw's uniform number."""
+    each), and the sampling parameters with the draw's uniform number.  ``num_pages``: the pages of every group's
+    pool (one number for all, or one per group); ``every``: per group, positions per cache row (None: one)."""
     import ctypes
 
     b = row_slot.shape[0]
@@ -424,9 +506,16 @@ def step_from_state(row_slot: torch.Tensor, fresh: torch.Tensor, fresh_values: t
     g = len(tables)
     table_ptrs = (ctypes.c_void_p * max(g, 1))(*[t.data_ptr() for t in tables])
     slot_ptrs = (ctypes.c_void_p * max(g, 1))(*[k.data_ptr() for k in kv_slots])
+    pages = [int(num_pages)] * g if isinstance(num_pages, int) else [int(n) for n in num_pages]
+    rows_of = [1] * g if every is None else [int(e) for e in every]
+    if len(pages) != g or len(rows_of) != g:
+        raise ValueError("one page count and one row stride per page group")
+    page_counts = (ctypes.c_int * max(g, 1))(*pages)
+    strides = (ctypes.c_int * max(g, 1))(*rows_of)
     check(library().cw_step_from_state(
         _ptr(row_slot), _ptr(fresh), _ptr(fresh_values), _ptr(state), state.shape[1], b, int(page_size), int(max_blocks),
-        int(num_pages), g, ctypes.cast(table_ptrs, ctypes.c_void_p), ctypes.cast(slot_ptrs, ctypes.c_void_p), _ptr(tokens),
+        max(pages, default=1), g, ctypes.cast(page_counts, ctypes.c_void_p), ctypes.cast(strides, ctypes.c_void_p),
+        ctypes.cast(table_ptrs, ctypes.c_void_p), ctypes.cast(slot_ptrs, ctypes.c_void_p), _ptr(tokens),
         _ptr(positions), _ptr(ctx_lens), _ptr(tok_seq), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
         _ptr(status), _stream()), "step_from_state")
 

@@ -34,21 +34,28 @@ def per_head_product(a: torch.Tensor, a_head_width: int, w: torch.Tensor, out: t
     return out
 
 
-SCORE_CHOSEN, SCORE_ALL = 0, 1
+SCORE_CHOSEN, SCORE_ALL, SCORE_SIGMOID = 0, 1, 2
 
 
 def moe_choose(logits: torch.Tensor, bias: torch.Tensor | None, tok_seq: torch.Tensor, top: int, scoring: int = SCORE_CHOSEN,
-               groups: int = 1, keep: int = 1):
+               groups: int = 1, keep: int = 1, correction: torch.Tensor | None = None, weight_scale: float = 1.0,
+               group_rank: int = 1):
     """(chosen experts int32 [N, top], their weights float32 [N, top]) from float32 router logits [N, E] (+ bias): the
     ``top`` largest, weighted by the softmax over the chosen ones (``SCORE_CHOSEN``) or by their shares of the softmax
-    over all experts, not renormalised (``SCORE_ALL``); with ``groups`` > 1 only experts of the ``keep`` best of ``groups``
-    equal runs of neighbours can be chosen (a run counts as its largest entry); padding rows choose -1."""
+    over all experts, not renormalised (``SCORE_ALL``); ``SCORE_SIGMOID``: an expert's score is the sigmoid of its logit,
+    experts are ranked by score + ``correction`` [E] and weighted by the score alone.  With ``groups`` > 1 only experts of
+    the ``keep`` best of ``groups`` equal runs of neighbours can be chosen (a run counts as the sum of its ``group_rank``
+    largest entries).  Every weight is multiplied by ``weight_scale``.  Padding rows choose -1."""
     _need(logits, torch.float32, "logits", 2)
     n, e = logits.shape
+    if correction is not None:
+        _need(correction, torch.float32, "correction", 1)
+        if correction.shape[0] != e or scoring != SCORE_SIGMOID:
+            raise ValueError("a correction per expert goes with sigmoid scores")
     sel = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     wt = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     check(library().cw_moe_choose(_ptr(logits), _ptr(bias), _ptr(tok_seq), _ptr(sel), _ptr(wt), n, e, top, int(scoring), int(groups), int(keep),
-                                  _stream()), "moe_choose")
+                                  _ptr(correction), float(weight_scale), int(group_rank), _stream()), "moe_choose")
     return sel, wt
 
 

@@ -29,7 +29,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_sample_state": [P, P, P, P, P, P, I, I, LL, P, P, I, P],
     "cw_sample_rows": [P, P, P, P, P, P, I, I, LL, P, P, I, P, P],
     "cw_sample_workspace_words": [I],
-    "cw_step_from_state": [P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P],
+    "cw_step_from_state": [P, P, P, P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, P, P, P, P, P, P],
     # layers with a state of fixed size (csrc/recurrence.cu)
     "cw_shift_mix": [P, P, P, LL, LL, P, P, P, P, I, I, I, I, P],
     "cw_causal_conv": [P, I, P, P, P, LL, LL, P, P, P, P, I, I, I, P],
@@ -43,7 +43,13 @@ _SIGNATURES: dict[str, list] = {
     # attention over a window of rows [key | value] (csrc/window_attention.cu); absolute positions and the sum of two normed
     # contributions (csrc/embed_norm.cu)
     "cw_store_rows": [P, I, I, I, P, P, I, LL, I, P, P],
-    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, I, P, P, I, P, P, I, I, P, P],
+    "cw_window_attention": [P, I, P, P, I, I, I, P, P, I, I, I, I, I, I, F, P, P, P, I, I, P, P, I, P, P, I, I, P,
+                            F, P, F, I, P, I, I, P, P, I, I, P],
+    "cw_pool_rows": [P, P, I, I, I, P, P, P, P, LL, I, I, I, I, P, P],
+    "cw_pair_embed_add": [P, P, P, P, P, P, P, LL, P, I, LL, LL, I, I, I, I, I, P, P],
+    "cw_axpy_rmsnorm": [P, P, P, F, F, P, P, P, F, I, I, I, P],
+    "cw_depth_average": [P, P, P, F, F, P, LL, I, P, P, P, P, F, I, I, I, P],
+    "cw_bounded_forget": [P, I, P, P, P, I, I, P],
     "cw_rotate_store": [P, I, P, P, P, P, I, I, I, I, I, I, P, P, LL, I, P, P],
     "cw_window_attention_set_mma": [I],
     "cw_scale_add_sinusoid": [P, P, P, F, I, I, P],
@@ -54,7 +60,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_grouped_gemm": [P, I, I, P, P, LL, P, I, I, P, P, I, P, P, I, I, I, I, I, I, F, I, P],
     "cw_grouped_gemm_set_mma": [I],
     "cw_latent_attention_set_mma": [I],
-    "cw_moe_choose": [P, P, P, P, P, I, I, I, I, I, I, P],
+    "cw_moe_choose": [P, P, P, P, P, I, I, I, I, I, I, P, F, I, P],
     "cw_moe_group": [P, P, P, P, I, I, P],
     "cw_moe_combine": [P, P, P, P, I, I, I, P],
     # the delta rule, the gates and the read-out of a matrix memory (csrc/recurrence_gated.cu)

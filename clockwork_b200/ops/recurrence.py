@@ -14,7 +14,7 @@ from .library import check, library
 
 FORM_CHANNEL_DECAY, FORM_STEP_SIZE, FORM_CHANNEL_DECAY_AFTER, FORM_HEAD_DECAY, FORM_GATED_WITH_KEY_SUM = 0, 1, 2, 3, 4
 ACT_GELU_TANH, ACT_TANH, ACT_SILU, ACT_SIGMOID = 0, 1, 2, 3
-GATE_SILU, GATE_SIGMOID = 0, 1
+GATE_SILU, GATE_SIGMOID, GATE_NONE = 0, 1, 2
 
 
 def _state_args(view) -> tuple:
@@ -188,6 +188,22 @@ def sigmoid_power_decay_(pre: torch.Tensor, tau: float) -> torch.Tensor:
     return pre
 
 
+def bounded_forget_(proj: torch.Tensor, channels: int, bias: torch.Tensor | None, lower: torch.Tensor) -> torch.Tensor:
+    """In place on float32 ``proj`` [N, >= 2*channels] = ``[q | z | ..]``: ``q <- silu(q)`` and ``z <- f = lower + (1 - lower)
+    sigmoid(z + bias)``, forget gates that never fall below ``lower`` [channels]; returns ``1 - f`` as float32 [N, channels]
+    (what a channel of the state takes of the new value)."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] < 2 * channels:
+        raise ValueError("proj must be float32 [N, >= 2*channels] with unit column stride")
+    _need(lower, torch.float32, "lower", 1)
+    if lower.shape[0] != channels or (bias is not None and bias.shape[0] != channels):
+        raise ValueError(f"lower and bias must have {channels} entries")
+    n = proj.shape[0]
+    take = torch.empty((n, channels), dtype=torch.float32, device=proj.device)
+    check(library().cw_bounded_forget(_ptr(proj), proj.stride(0) if n > 1 else max(proj.stride(0), proj.shape[1]), _ptr(bias), _ptr(lower),
+                                      _ptr(take), n, channels, _stream()), "bounded_forget")
+    return take
+
+
 def activation_cols_(x: torch.Tensor, cols: int, kind: int) -> torch.Tensor:
     """In place on the first ``cols`` columns of every row of ``x`` [N, C] (unit column stride)."""
     if x.dim() != 2 or x.stride(1) != 1 or not 0 <= cols <= x.shape[1]:
@@ -198,20 +214,24 @@ def activation_cols_(x: torch.Tensor, cols: int, kind: int) -> torch.Tensor:
     return x
 
 
-def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float, gate_first: bool,
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor | None, weight: torch.Tensor, parts: int, eps: float, gate_first: bool,
                      out_dtype: torch.dtype, gate: int = GATE_SILU, shared_weight: bool = False) -> torch.Tensor:
     """``gate_first``: norm_parts(y * gate(z)) * weight; else norm_parts(y) * weight * gate(z).  y, z float32.
-    ``gate``: silu or sigmoid.  ``shared_weight``: ``weight`` has one part's width and every part uses it."""
+    ``gate``: silu or sigmoid, or ``GATE_NONE`` (``z`` None: norm_parts(y) * weight).  ``shared_weight``: ``weight`` has one
+    part's width and every part uses it."""
     _need(y, torch.float32, "y", 2)
-    if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1:
+    if (z is None) != (gate == GATE_NONE):
+        raise ValueError("GATE_NONE goes with z = None")
+    if z is not None and (z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1):
         raise ValueError("z must be float32 [N, C] with unit column stride")
     _need(weight, torch.float32, "weight", 1)
     n, c = y.shape
     if weight.shape[0] != (c // parts if shared_weight else c):
         raise ValueError(f"weight of {weight.shape[0]} for {parts} parts of {c} columns")
     out = torch.empty((n, c), dtype=out_dtype, device=y.device)
-    mode = (1 if gate_first else 0) | (2 if gate == GATE_SIGMOID else 0) | (4 if shared_weight else 0)
-    check(library().cw_gated_group_norm(_ptr(y), _ptr(z), z.stride(0) if n > 1 else max(z.stride(0), c), _ptr(weight), _ptr(out), n, c,
+    mode = (1 if gate_first else 0) | (2 if gate == GATE_SIGMOID else 0) | (4 if shared_weight else 0) | (8 if z is None else 0)
+    ldz = 0 if z is None else (z.stride(0) if n > 1 else max(z.stride(0), c))
+    check(library().cw_gated_group_norm(_ptr(y), _ptr(z), ldz, _ptr(weight), _ptr(out), n, c,
                                         parts, float(eps), mode, dtype_code(out_dtype), _stream()),
           "gated_group_norm")
     return out

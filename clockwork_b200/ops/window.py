@@ -70,6 +70,27 @@ def rotate_store(src: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tens
     return q
 
 
+NO_WINDOW = 1 << 30  # a window that never closes: every earlier position is seen
+
+
+def pool_rows(cache_rows: torch.Tensor, block_tables: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor,
+              pool_slots: torch.Tensor, pool_cache: torch.Tensor, pool: int, status: torch.Tensor) -> None:
+    """For every token whose position ends a block of ``pool`` positions ((position + 1) % pool == 0): the mean of the block's
+    rows of ``cache_rows`` [pages, page_size, kv_heads, width] (through the request's ``block_tables`` row) is written to row
+    ``pool_slots[n]`` of ``pool_cache`` [pages', page_size, kv_heads, width].  The sum is float32, in position order."""
+    _need(cache_rows, None, "cache", 4)
+    _need(pool_cache, cache_rows.dtype, "pool cache", 4)
+    if tuple(pool_cache.shape[1:]) != tuple(cache_rows.shape[1:]):
+        raise ValueError(f"pool cache rows {tuple(pool_cache.shape)} do not match cache rows {tuple(cache_rows.shape)}")
+    _need(block_tables, torch.int32, "block_tables", 2)
+    _need(pool_slots, torch.int32, "pool_slots", 1)
+    n = positions.shape[0]
+    width = cache_rows.shape[2] * cache_rows.shape[3]
+    check(library().cw_pool_rows(_ptr(cache_rows), _ptr(block_tables), block_tables.shape[1], cache_rows.shape[1], cache_rows.shape[0],
+                                 _ptr(positions), _ptr(tok_seq), _ptr(pool_slots), _ptr(pool_cache), pool_cache.shape[0] * pool_cache.shape[1],
+                                 width, int(pool), n, dtype_code(cache_rows.dtype), _ptr(status), _stream()), "pool_rows")
+
+
 def window_parts(num_tokens: int, window: int, dtype: torch.dtype) -> int:
     """In how many pieces the keys of a row are cut (the pieces are added up by a second kernel).  float32 runs never
     cut: their results do not depend on the step's size to the last bit.  bfloat16: finely when a step has so few
@@ -91,11 +112,18 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
                      tok_seq: torch.Tensor, q_start: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, window: int, scale: float,
                      head_scale: torch.Tensor | None, talk: torch.Tensor | None, head_bias: torch.Tensor | None,
                      sigmoid_weights: bool, status: torch.Tensor, parts: int = 1, blocked: bool = False,
-                     sink: torch.Tensor | None = None) -> torch.Tensor:
+                     sink: torch.Tensor | None = None, softcap: float = 0.0, slopes: torch.Tensor | None = None,
+                     temperature: tuple | None = None, gate: torch.Tensor | None = None, pool: int = 0,
+                     pool_rows_cache: torch.Tensor | None = None, pool_tables: torch.Tensor | None = None) -> torch.Tensor:
     """[N, heads*dv] in ``q``'s dtype.  ``q`` [N, >= heads*dk] (queries in the leading columns, unit column stride);
     ``cache_rows`` [pages, page_size, kv_heads, dk + dv]; the step's tokens are already stored there.  ``blocked``:
     positions are cut into blocks of ``window`` and a token sees its own block up to itself, instead of the last
-    ``window`` positions.  ``sink`` [heads]: a logit per head that enters the softmax's denominator once."""
+    ``window`` positions.  ``sink`` [heads]: a logit per head that enters the softmax's denominator once.  ``softcap``:
+    the score becomes ``softcap tanh(score / softcap)``; ``slopes`` [heads]: ``slopes[h] * (distance to the key)`` is taken
+    off the (capped) score; ``temperature`` = (coef, every): the scores of a query at position p are first multiplied by
+    ``1 + coef ln(floor((p + 1) / every) + 1)``; ``gate`` float32 [N, >= heads] (unit column stride): head h's output is
+    multiplied by ``sigmoid(gate[n, h])``; ``pool``: every block of ``pool`` positions that ends at or before p - window is
+    seen as one more key and value, row b of the request in ``pool_rows_cache`` (through ``pool_tables``)."""
     if q.dim() != 2 or q.stride(1) != 1 or q.shape[1] < heads * dk:
         raise ValueError("q must be [N, >= heads*dk] with unit column stride")
     _need(cache_rows, q.dtype, "cache", 4)
@@ -112,6 +140,18 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
             if t.numel() != size:
                 raise ValueError(f"{name} has {t.numel()} numbers, {size} expected")
     n = q.shape[0]
+    if slopes is not None:
+        _need(slopes, torch.float32, "slopes", 1)
+        if slopes.shape[0] != heads:
+            raise ValueError(f"slopes has {slopes.shape[0]} numbers for {heads} heads")
+    if gate is not None and (gate.dtype != torch.float32 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[1] < heads or gate.shape[0] != n):
+        raise ValueError("gate must be float32 [N, >= heads] with unit column stride")
+    if pool:
+        _need(pool_rows_cache, q.dtype, "pool cache", 4)
+        _need(pool_tables, torch.int32, "pool_tables", 2)
+        if tuple(pool_rows_cache.shape[1:]) != tuple(cache_rows.shape[1:]) or pool_tables.shape[0] != block_tables.shape[0]:
+            raise ValueError("the pooled rows' cache and tables must match the cache's rows and the step's requests")
+    coef, every = temperature if temperature is not None else (0.0, 0)
     out = torch.empty((n, heads * dv), dtype=q.dtype, device=q.device)
     partial = None
     if parts > 1:
@@ -123,5 +163,8 @@ def window_attention(q: torch.Tensor, cache_rows: torch.Tensor, block_tables: to
         cache_rows.shape[1], cache_rows.shape[0], _ptr(positions), _ptr(tok_seq), n, heads, kv_heads, dk, dv, int(window), float(scale),
         _ptr(head_scale), _ptr(talk), _ptr(head_bias), 1 if sigmoid_weights else 0, 1 if blocked else 0, _ptr(sink), _ptr(out), parts,
         _ptr(partial),
-        _ptr(q_start), q_start.shape[0] - 1, dtype_code(q.dtype), _ptr(status), _stream()), "window_attention")
+        _ptr(q_start), q_start.shape[0] - 1, dtype_code(q.dtype), _ptr(status),
+        float(softcap), _ptr(slopes), float(coef), int(every), _ptr(gate), (gate.stride(0) if n > 1 else max(gate.stride(0), gate.shape[1])) if gate is not None else 0,
+        int(pool), _ptr(pool_rows_cache) if pool else None, _ptr(pool_tables) if pool else None, pool_tables.shape[1] if pool else 0,
+        pool_rows_cache.shape[0] if pool else 0, _stream()), "window_attention")
     return out

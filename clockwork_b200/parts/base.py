@@ -39,13 +39,16 @@ class PagedKVNeed:
     into blocks of ``block`` and a token reads its own block only (pages of earlier blocks can be given back).
     ``planes``: 2 for
     keys and values; 1 for a mixer that keeps one row per token (a latent that keys and values are both
-    made from): its view's ``k_cache`` and ``v_cache`` are then the same tensor."""
+    made from): its view's ``k_cache`` and ``v_cache`` are then the same tensor.  ``every``: the mixer keeps one row per
+    ``every`` positions (a summary of each whole block of that many): row r belongs to positions r*every .. r*every +
+    every - 1, and the slot that a step names for a token is the row of the token's block; no window."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     planes: int = 2
     block: int | None = None
+    every: int = 1
 
 
 @dataclass(frozen=True)
@@ -121,6 +124,11 @@ class ResidualStream:
         self.pending = None     # a tensor [N, H], or the ``ops.PartialSums`` of a product (for norms that take them)
         self.next_norm = None   # the Norm part that will read the residual next, if the block knows it
         self.half_norm = None   # (norm weight, x * weight in bfloat16, per-row partial sums of squares)
+        # for models whose blocks read earlier layers' outputs (``ModelSpec.keeps_layer_outputs``):
+        self.layer_outputs = None  # float32 [runs + 1, N, H]: plane 0 the input rows, plane r + 1 what layer run r left
+        self.runs_done = 0         # layer runs finished so far
+        self.normed = None         # (norm part, its output for the residual as it stands): a block that already ran the next norm
+        self.spare = None          # a second [N, H] buffer for blocks that must not overwrite the rows they read
 
     def push(self, delta: torch.Tensor | None) -> None:
         if delta is None:
@@ -128,7 +136,7 @@ class ResidualStream:
         if self.pending is not None:
             self.flush()
         self.pending = delta
-        self.half_norm = None
+        self.half_norm = self.normed = None
 
     def flush(self) -> None:
         if self.pending is not None:
@@ -136,12 +144,12 @@ class ResidualStream:
 
             ops.add_to_residual(self.residual, self.pending)
             self.pending = None
-            self.half_norm = None
+            self.half_norm = self.normed = None
 
     def residual_after_flush(self) -> torch.Tensor:
         """The float32 residual with nothing pending: what a fused epilogue adds into."""
         self.flush()
-        self.half_norm = None  # the caller is about to change the residual
+        self.half_norm = self.normed = None  # the caller is about to change the residual
         return self.residual
 
     def norm_weight_to_begin(self) -> torch.Tensor | None:
@@ -223,9 +231,9 @@ class Mixer(Part):
     takes_half_normed = False  # True: ``x`` may be an ``ops.gemm.RowScaled`` (it only feeds matrix products)
 
     def cache_need(self) -> PagedKVNeed | SlotStateNeed | tuple | None:
-        """What the mixer keeps per request.  A mixer made of several (``side_by_side``) returns a tuple of
-        needs, at most one of them pages and at most one a state slot, and is handed a tuple of views in the
-        same order."""
+        """What the mixer keeps per request.  A mixer that keeps several things (one made of several mixers, or one
+        with two kinds of rows) returns a tuple of needs, different paged needs and at most one state slot, and is
+        handed a tuple of views in the same order."""
         return None
 
     def mix(self, ctx: StepContext, x: torch.Tensor, view) -> torch.Tensor:

@@ -11,10 +11,14 @@ output is the weighted sum of the chosen experts' outputs, added into the float3
 of the choices.  Tokens are grouped by expert on the device (no host round trip), so the part is safe
 to capture in a CUDA graph.  Parameters: ``hidden_size, expert_size, experts, top``, and optionally
 
-* ``scoring``: ``"chosen"`` (the default, as above) or ``"all"``: the weights are the chosen experts' shares of the
-  softmax over all experts, not renormalised;
-* ``groups, keep``: the experts lie in ``groups`` equal runs of neighbours, a run counts as its best expert, and only
-  experts of the ``keep`` best runs can be chosen;
+* ``scoring``: ``"chosen"`` (the default, as above), ``"all"``: the weights are the chosen experts' shares of the
+  softmax over all experts, not renormalised, or ``"sigmoid"``: an expert's score is the sigmoid of its logit, and the
+  weights are the chosen experts' scores, not renormalised;
+* ``correction`` (with ``"sigmoid"``): experts are ranked, alone and in their runs, by score + ``correction[e]`` (tensor
+  ``correction`` [E]); the weights do not contain it;
+* ``weight_scale``: every weight is multiplied by it;
+* ``groups, keep``: the experts lie in ``groups`` equal runs of neighbours and only experts of the ``keep`` best runs can
+  be chosen; a run counts as the sum of its ``group_rank`` largest entries (1, the default: as its best expert);
 * ``limit``: a positive number selects the clamped activation ``a sigmoid(1.702 a) (b + 1)`` with ``a = min(gate(x),
   limit)`` and ``b = clamp(up(x), -limit, limit)`` instead of ``silu(gate(x)) up(x)``;
 * ``router_bias``: whether the router has a bias (tensor ``router.b``; the default) or not;
@@ -76,10 +80,18 @@ class MixtureOfExperts(FeedForward):
         if not 0 < self.top <= self.experts:
             raise ValueError(f"top {self.top} must lie in 1..experts ({self.experts})")
         scoring = str(spec.get("scoring", "chosen"))
-        if scoring not in ("chosen", "all"):
-            raise ValueError(f"scoring must be 'chosen' or 'all', got {scoring!r}")
-        self.scoring = grouped_ops.SCORE_ALL if scoring == "all" else grouped_ops.SCORE_CHOSEN
+        modes = {"chosen": grouped_ops.SCORE_CHOSEN, "all": grouped_ops.SCORE_ALL, "sigmoid": grouped_ops.SCORE_SIGMOID}
+        if scoring not in modes:
+            raise ValueError(f"scoring must be one of {sorted(modes)}, got {scoring!r}")
+        self.scoring = modes[scoring]
+        self.has_correction = bool(spec.get("correction", False))
+        if self.has_correction and scoring != "sigmoid":
+            raise ValueError("a correction per expert goes with sigmoid scores")
+        self.weight_scale = float(spec.get("weight_scale", 1.0))
         self.groups, self.keep = int(spec.get("groups", 1)), int(spec.get("keep", 1))
+        self.group_rank = int(spec.get("group_rank", 1))
+        if not 1 <= self.group_rank <= min(4, max(1, int(spec["experts"]) // max(1, self.groups))):
+            raise ValueError(f"group_rank {self.group_rank} must lie in 1..4 and within a run of experts")
         if self.groups < 1 or self.experts % self.groups or not 1 <= self.keep <= self.groups:
             raise ValueError(f"{self.experts} experts do not lie in {self.groups} equal groups of which {self.keep} are kept")
         if self.keep * (self.experts // self.groups) < self.top:
@@ -89,7 +101,7 @@ class MixtureOfExperts(FeedForward):
         shared = spec.get("shared")
         self.shared_size = int(shared["size"]) if shared else 0
         self.shared_limit = float(shared.get("limit") or 0.0) if shared else 0.0
-        self.w_gate = self.w_up = self.w_down = self.router = self.router_bias = None
+        self.w_gate = self.w_up = self.w_down = self.router = self.router_bias = self.correction = None
         self.shared_gate = self.shared_up = self.shared_down = None
 
     def tensor_decls(self):
@@ -101,6 +113,8 @@ class MixtureOfExperts(FeedForward):
         yield TensorDecl(self.name("router"), (self.experts, h), "matrix", "linear")
         if self.has_router_bias:
             yield TensorDecl(self.name("router.b"), (self.experts,), "vector", "bias")
+        if self.has_correction:
+            yield TensorDecl(self.name("correction"), (self.experts,), "vector", "bias")
         if self.shared_size:
             yield TensorDecl(self.name("shared.gate"), (self.shared_size, h), "matrix", "linear")
             yield TensorDecl(self.name("shared.up"), (self.shared_size, h), "matrix", "linear")
@@ -111,6 +125,7 @@ class MixtureOfExperts(FeedForward):
         self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
         self.router = Linear(fetch(self.name("router")))
         self.router_bias = fetch(self.name("router.b")) if self.has_router_bias else None
+        self.correction = fetch(self.name("correction")).contiguous() if self.has_correction else None
         if self.shared_size:
             self.shared_gate = fetch(self.name("shared.gate")).unsqueeze(0).contiguous()  # one "expert" that every row goes through
             self.shared_up = fetch(self.name("shared.up")).unsqueeze(0).contiguous()
@@ -119,7 +134,8 @@ class MixtureOfExperts(FeedForward):
     def _routed(self, ctx: StepContext, x):
         """(the chosen experts' outputs float32 [N*top, hidden] in choice order, the choices, their weights)."""
         sel, weights = grouped_ops.moe_choose(self.router.to_float32(x), self.router_bias, ctx.tok_seq, self.top, self.scoring,
-                                              self.groups, self.keep)
+                                              self.groups, self.keep, correction=self.correction, weight_scale=self.weight_scale,
+                                              group_rank=self.group_rank)
         offsets, order = grouped_ops.moe_group(sel, self.experts)
         act = grouped_ops.expert_gate_up(x, self.w_gate, self.w_up, offsets, order, self.top, self.limit)
         return grouped_ops.expert_down(act, self.w_down, offsets, order), sel, weights

@@ -32,6 +32,12 @@ class DecoderModel:
         self.absolute_positions = None
         if spec.absolute_positions is not None:
             self.absolute_positions = build_part("position", spec.absolute_positions, "", dtype, self.device)
+        # a part that adds a row chosen by (previous token, token): its state (the previous token of every request) lives in
+        # a cache layer of its own, above every layer's
+        self.pair_embedding = None
+        self.pair_cache_layer = max([len(spec.layers)] + [s.resolved_cache_layer() + 1 for s in spec.schedule])
+        if spec.pair_embedding is not None:
+            self.pair_embedding = build_part("embedding", spec.pair_embedding, "", dtype, self.device)
         self.embedding: torch.Tensor | None = None
         self.head: Linear | None = None
 
@@ -50,12 +56,15 @@ class DecoderModel:
                 raise ValueError(
                     f"layer {step.layer} reads cache layer {cache_layer}, whose contents have another shape"
                 )
+        if self.pair_embedding is not None:
+            needs[self.pair_cache_layer] = self.pair_embedding.cache_need()
         return needs
 
     def graph_safe(self) -> bool:
         """Whether a step of this model may be captured in a CUDA graph."""
         return (all(block.graph_safe for block in self.blocks) and self.final_norm.graph_safe
-                and (self.absolute_positions is None or self.absolute_positions.graph_safe))
+                and (self.absolute_positions is None or self.absolute_positions.graph_safe)
+                and (self.pair_embedding is None or self.pair_embedding.graph_safe))
 
     def graph_safe_portions(self) -> bool:
         """Whether a step of this model that holds prompt portions may be captured in a CUDA graph."""
@@ -68,6 +77,8 @@ class DecoderModel:
         yield self.final_norm
         if self.absolute_positions is not None:
             yield self.absolute_positions
+        if self.pair_embedding is not None:
+            yield self.pair_embedding
 
     def step_scalars(self) -> dict:
         """The per-step device scalars that the model's parts declare (``Part.step_scalars``), by name."""
@@ -94,6 +105,8 @@ class DecoderModel:
     def tensor_decls(self) -> list[TensorDecl]:
         spec = self.spec
         decls = [TensorDecl(spec.embedding_name, (spec.vocab_size, spec.hidden_size), "table", "embedding")]
+        if self.pair_embedding is not None:
+            decls.extend(self.pair_embedding.tensor_decls())
         for block in self.blocks:
             decls.extend(block.tensor_decls())
         decls.extend(self.final_norm.tensor_decls())
@@ -104,6 +117,8 @@ class DecoderModel:
 
     def load_weights(self, fetch) -> None:
         self.embedding = fetch(self.spec.embedding_name)
+        if self.pair_embedding is not None:
+            self.pair_embedding.load_weights(fetch)
         for block in self.blocks:
             block.load_weights(fetch)
         self.final_norm.load_weights(fetch)
@@ -129,6 +144,7 @@ class DecoderModel:
                     visit(value)
 
         visit(self.blocks)
+        visit(self.pair_embedding)
         visit(self.final_norm)
         visit(self.head)
         return sum(seen.values())
@@ -141,10 +157,18 @@ class DecoderModel:
         # only just written those inputs, the first kernel here must not start before it has finished)
         # (a position part multiplies the rows by the embedding's scale itself; without one the gather does)
         scale = 1.0 if self.absolute_positions is not None else self.spec.embedding_scale
-        stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status, serial=ctx.inputs_from_device, scale=scale))
+        schedule = self.spec.schedule
+        planes = None
+        if self.spec.keeps_layer_outputs:
+            # the input rows and what every layer run leaves, a plane each: the embedding is gathered into plane 0
+            planes = torch.empty((len(schedule) + 1, token_ids.shape[0], self.spec.hidden_size), dtype=torch.float32, device=self.device)
+        stream = ResidualStream(ops.embed(self.embedding, token_ids, ctx.status, serial=ctx.inputs_from_device, scale=scale,
+                                          out=None if planes is None else planes[0]))
+        stream.layer_outputs = planes
         if self.absolute_positions is not None:
             self.absolute_positions.add_to_embedding(stream.residual, ctx.positions, self.spec.embedding_scale)
-        schedule = self.spec.schedule
+        if self.pair_embedding is not None:
+            self.pair_embedding.add_to_embedding(ctx, stream.residual, token_ids, ctx.views[self.pair_cache_layer])
         for i, step in enumerate(schedule):
             view = ctx.views.get(step.resolved_cache_layer())
             if view is not None and hasattr(view, "write"):

@@ -9,7 +9,7 @@ import torch
 
 from ..config.model_spec import LayerSpec, PartSpec
 
-_KINDS: dict[str, dict[str, Callable]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}}
+_KINDS: dict[str, dict[str, Callable]] = {"norm": {}, "position": {}, "mixer": {}, "ffn": {}, "block": {}, "embedding": {}}
 
 
 def _register(category: str, kind: str, cls, replace: bool) -> None:
@@ -37,6 +37,11 @@ def register_ffn(kind: str, cls, *, replace: bool = False) -> None:
 
 def register_block(kind: str, cls, *, replace: bool = False) -> None:
     _register("block", kind, cls, replace)
+
+
+def register_embedding(kind: str, cls, *, replace: bool = False) -> None:
+    """Parts that add to the embedding rows (``add_to_embedding(ctx, x, token_ids, view)``)."""
+    _register("embedding", kind, cls, replace)
 
 
 def registered(category: str) -> list[str]:

@@ -46,6 +46,9 @@ class RMSNorm(Norm):
         return self.weight if self.dtype == torch.bfloat16 else None
 
     def forward(self, stream: ResidualStream, status: torch.Tensor, lazy: bool = False):
+        ready, stream.normed = stream.normed, None
+        if ready is not None and ready[0] is self and stream.pending is None:
+            return ready[1]  # the block before already ran this norm on the residual as it stands
         half, stream.half_norm = stream.half_norm, None
         if lazy and half is not None and stream.pending is None and half[0] is self.weight:
             # the product that wrote the residual began this norm; the product that reads it finishes it
@@ -59,6 +62,15 @@ class RMSNorm(Norm):
         """``residual += norm(sum of factor * tensor over the terms) * weight``: this norm behind a sublayer, whose output
         comes as one or two pairs (float32 [N, size], factor).  Statistics, sum and residual are float32."""
         ops.sum_rmsnorm_add(stream.residual_after_flush(), terms, self.weight, self.eps)
+
+    def scaled_add(self, x: torch.Tensor, terms, into: torch.Tensor | None = None) -> torch.Tensor:
+        """``y = x + sum of factor * tensor over the terms`` (float32; one or two pairs) goes to ``into`` (``x`` itself when
+        None); returns this norm of ``y``."""
+        return ops.axpy_rmsnorm(x, terms, self.weight, self.eps, self.dtype, into)
+
+    def weight_and_eps(self) -> tuple:
+        """(weight, eps) for a kernel that runs this norm at the end of other work."""
+        return self.weight, self.eps
 
     def forward_rows(self, stream: ResidualStream, rows: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
         stream.flush()

@@ -46,6 +46,12 @@ token), ``S <- exp(lf + m_(t-1) - m_t) S + exp(li - m_t) k v^T`` and the same fo
 (max(|n . q|, exp(-m_t)) + 1e-6)``.  Each head's o is divided by its root mean square, times ``norm`` (all heads' width),
 times ``sigmoid(W_g x)``, and goes through ``o``.  The state slot holds S with n as one more value column, and m.
 
+``hgrn2`` (linear attention whose forget gate also decides what is written).  Parameters: ``hidden_size, heads, dim, vdim,
+eps``.  ``q = silu(W_q x)``, ``v = W_v x``, ``f = l + (1 - l) sigmoid(W_f x + b_f)`` per head and key channel with the lower
+bound ``l`` (tensor ``lower`` [heads*dim]); per head ``S <- diag(f) S + (1 - f) v^T``, ``o = S^T q`` (after the update; there is
+no key and no other scale).  Each head's o is divided by its root mean square over vdim, times ``norm`` (vdim entries, shared
+by the heads), and goes through ``o``.  The state slot holds S.
+
 All run the recurrence itself, the decays, step sizes and norms in float32 in either run precision;
 the products that feed them write float32.  ``mix`` returns the output product as float32 for a mixer that
 stands beside another (``side_by_side``).
@@ -272,6 +278,59 @@ class DecayLinearMixer(_LinearAttention):
         return rec_ops.gated_group_norm(o, g, self.norm_w, 1, self.eps, False, self.dtype, gate=rec_ops.GATE_SIGMOID)
 
 
+class BoundedForgetMixer(Mixer):
+    """``hgrn2``: see the module's text.  One product for ``[q | f | v]`` with float32 output; one kernel makes silu(q), the
+    gates f and 1 - f; the scan is the one of ``gated_linear`` with 1 - f in the key's place."""
+
+    graph_safe = True
+    graph_safe_portions = True
+
+    def __init__(self, spec, prefix, dtype, device) -> None:
+        super().__init__(spec, prefix, dtype, device)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.heads, self.dim, self.vdim = int(p["heads"]), int(p["dim"]), int(p["vdim"])
+        self.eps = float(p["eps"])
+        if min(self.heads, self.dim, self.vdim) <= 0:
+            raise ValueError("heads, dim and vdim must be positive")
+        self.qk, self.inner = self.heads * self.dim, self.heads * self.vdim
+
+    def cache_need(self) -> SlotStateNeed:
+        return SlotStateNeed((self.heads * self.dim * self.vdim,))
+
+    def tensor_decls(self):
+        h = self.hidden_size
+        yield TensorDecl(self.name("q"), (self.qk, h), "matrix", "linear")
+        yield TensorDecl(self.name("f"), (self.qk, h), "matrix", "linear")
+        yield TensorDecl(self.name("f.b"), (self.qk,), "vector", "bias")
+        yield TensorDecl(self.name("lower"), (self.qk,), "vector", "unit_interval")
+        yield TensorDecl(self.name("v"), (self.inner, h), "matrix", "linear")
+        yield TensorDecl(self.name("norm"), (self.vdim,), "vector", "norm")
+        yield TensorDecl(self.name("o"), (h, self.inner), "matrix", "linear")
+
+    def load_weights(self, fetch) -> None:
+        self.w_in = Linear(torch.cat([fetch(self.name(s)) for s in ("q", "f", "v")], dim=0).contiguous())
+        self.f_bias = fetch(self.name("f.b")).contiguous()
+        self.lower = fetch(self.name("lower")).contiguous()
+        self.norm_w = fetch(self.name("norm")).contiguous()
+        self.o = Linear(fetch(self.name("o")))
+
+    def _normed_output(self, ctx: StepContext, x, view: StateView):
+        qk = self.qk
+        proj = self.w_in.to_float32(x)  # [N, q | f | v], float32
+        take = rec_ops.bounded_forget_(proj, qk, self.f_bias, self.lower)  # q <- silu(q), f in place, 1 - f
+        o = rec_ops.recurrence_scan(rec_ops.FORM_CHANNEL_DECAY_AFTER, q=proj[:, :qk], k=take, v=proj[:, 2 * qk :], pre=proj[:, qk : 2 * qk],
+                                    p0=None, p1=None, p2=None, view=view, offset=0, ctx=ctx, heads=self.heads, dk=self.dim, dv=self.vdim)
+        return rec_ops.gated_group_norm(o, None, self.norm_w, self.heads, self.eps, False, self.dtype, gate=rec_ops.GATE_NONE,
+                                        shared_weight=True)
+
+    def mix(self, ctx: StepContext, x, view: StateView):
+        return self.o.to_float32(self._normed_output(ctx, x, view))
+
+    def forward(self, ctx: StepContext, x, view: StateView, stream: ResidualStream):
+        return self.o.add_or_defer(self._normed_output(ctx, x, view), stream)
+
+
 class ChannelDeltaMixer(Mixer):
     graph_safe = True
     graph_safe_portions = True
@@ -396,6 +455,7 @@ class MatrixMemoryMixer(Mixer):
         return self.o.add_or_defer(self._gated_output(ctx, x, view), stream)
 
 
+register_mixer("hgrn2", BoundedForgetMixer, replace=True)
 register_mixer("channel_delta", ChannelDeltaMixer, replace=True)
 register_mixer("matrix_memory", MatrixMemoryMixer, replace=True)
 register_mixer("gated_linear", GatedLinearMixer, replace=True)

@@ -16,8 +16,10 @@ from dataclasses import dataclass
 ROLES = ("matrix", "table", "vector", "index", "state32")
 
 # init -> distribution of the random-weights mode
-#   "linear"/"bias"/"embedding": N(0, 0.02);  "norm": 1 + N(0, 0.1);  "zeros"; "index": arange
-INITS = ("linear", "bias", "embedding", "norm", "zeros", "index")
+#   "linear"/"bias"/"embedding": N(0, 0.02);  "norm": 1 + N(0, 0.1);  "zeros"; "index": arange;
+#   "unit_interval": sigmoid of N(0, 1), numbers between 0 and 1;  "mean_weights": (1 + N(0, 0.1)) / n for a last
+#   dimension of n (the weights of an average, roughly)
+INITS = ("linear", "bias", "embedding", "norm", "zeros", "index", "unit_interval", "mean_weights")
 
 
 @dataclass(frozen=True)

@@ -39,6 +39,10 @@ def draw_tensor(decl: TensorDecl, seed: int) -> torch.Tensor:
     values = rng.standard_normal(size=decl.shape, dtype=np.float32)
     if decl.init == "norm":
         values = np.float32(1.0) + np.float32(0.1) * values
+    elif decl.init == "unit_interval":
+        values = (np.float32(1.0) / (np.float32(1.0) + np.exp(-values))).astype(np.float32)
+    elif decl.init == "mean_weights":
+        values = ((np.float32(1.0) + np.float32(0.1) * values) / np.float32(decl.shape[-1])).astype(np.float32)
     else:  # linear, bias, embedding
         values = np.float32(0.02) * values
     return torch.from_numpy(values)
@@ -95,6 +99,10 @@ def fill_model_on_device(model, seed: int = 0) -> None:
         t.normal_(0.0, 1.0, generator=gen)
         if decl.init == "norm":
             t.mul_(0.1).add_(1.0)
+        elif decl.init == "unit_interval":
+            t.sigmoid_()
+        elif decl.init == "mean_weights":
+            t.mul_(0.1).add_(1.0).div_(decl.shape[-1])
         else:
             t.mul_(0.02)
         return t.to(dtype)
