@@ -374,7 +374,12 @@ def compare_designs(args) -> int:
     over blocks of 1,024 positions with rotation and a sink beside a matrix memory, a delta-rule layer in every fourth
     place, 32 routed experts of which a token uses 4 and a shared one, 7,168 feed-forward rows a token in all) beside
     Gamesun, the closest design the framework has (``gamesun-2k``: the same width, heads and layer count, two mixers side
-    by side in every layer, a gated feed-forward of 7,168).  With ``--layers N`` both models have N layers.  One JSON
+    by side in every layer, a gated feed-forward of 7,168).  With ``--design nuzulorn`` the design is Nuzulorn
+    (``nuzulorn-2k``: capped causal attention with a distance bias, attention over a window of 1,024 positions with blocks of
+    64 pooled before it, a recurrent layer with bounded forget gates in every fourth place, 32 routed experts of which a
+    token uses 4, 7,168 feed-forward rows a token, a hashed pair table and the average over the depth) beside Kapolorn, the
+    closest design the framework has (``kapolorn-2k``: the same width, heads and layer count, the same attention and
+    expert kernels).  With ``--layers N`` both models have N layers.  One JSON
     line; device time by CUDA events, medians."""
     import torch
 
@@ -384,7 +389,7 @@ def compare_designs(args) -> int:
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(0)
-    shape = {"rapitar": "rapitar-2k", "gamesun": "gamesun-2k", "kapolorn": "kapolorn-2k"}[args.design]
+    shape = {"rapitar": "rapitar-2k", "gamesun": "gamesun-2k", "kapolorn": "kapolorn-2k", "nuzulorn": "nuzulorn-2k"}[args.design]
     rapitar = shape_config(shape, args.layers)
     layers = len(rapitar["layers"])
     qwen = dict(QWEN25_1P5B, num_hidden_layers=layers, hidden_size=2048, num_attention_heads=16,
@@ -396,6 +401,8 @@ def compare_designs(args) -> int:
     beside = ("qwen2-2k", qwen, qwen["vocab_size"])
     if args.design == "kapolorn":
         beside = ("gamesun-2k", shape_config("gamesun-2k", layers), rapitar["vocab"])
+    if args.design == "nuzulorn":
+        beside = ("kapolorn-2k", shape_config("kapolorn-2k", layers), rapitar["vocab"])
     for name, raw, vocab in ((shape, rapitar, rapitar["vocab"]), beside):
         if args.model_filter and args.model_filter not in name:
             continue
@@ -463,7 +470,7 @@ def main() -> int:
     ap.add_argument("--top-k", type=int, default=-1)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (reported in config)")
-    ap.add_argument("--design", choices=["rapitar", "gamesun", "kapolorn"], default="rapitar", help="with --only designs: which design stands beside Qwen2")
+    ap.add_argument("--design", choices=["rapitar", "gamesun", "kapolorn", "nuzulorn"], default="rapitar", help="with --only designs: which design stands beside Qwen2")
     ap.add_argument("--model-filter", default="", help="with --only designs: run only the model whose name holds this text (profiling runs)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="qwen2.5-1.5b",

@@ -556,25 +556,30 @@ extern "C" int cw_moe_group(const int* sel, int* offsets, int* order, int* rank,
     return cw_launch_ordered(moe_group_kernel, dim3(1), dim3(1024), (size_t)(E + 1) * sizeof(int), stream, sel, offsets, order, rank, P, E);
 }
 
-// resid[n] += sum_t wt[n, t] * y[n * top + t] over the choices in order.
+// resid[n] += sum_t wt[n, t] * y[n * top + t] over the choices in order; with `assign` the sum replaces resid[n] (rows of no
+// request: zeros).
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ resid, const float* __restrict__ y, const int* __restrict__ sel,
-                   const float* __restrict__ wt, int W, int top) {
+                   const float* __restrict__ wt, int W, int top, int assign) {
     pdl_wait();
     const int row = blockIdx.x;
-    if (sel[(size_t)row * top] < 0) return;
+    if (sel[(size_t)row * top] < 0) {
+        if (assign)
+            for (int c = threadIdx.x; c < W; c += blockDim.x) resid[(size_t)row * W + c] = 0.f;
+        return;
+    }
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = 0.f;
         for (int t = 0; t < top; ++t) acc = fmaf(wt[(size_t)row * top + t], y[((size_t)row * top + t) * W + c], acc);
-        resid[(size_t)row * W + c] += acc;
+        resid[(size_t)row * W + c] = assign ? acc : resid[(size_t)row * W + c] + acc;
     }
 }
 
-extern "C" int cw_moe_combine(float* resid, const float* y, const int* sel, const float* wt, int N, int W, int top,
+extern "C" int cw_moe_combine(float* resid, const float* y, const int* sel, const float* wt, int N, int W, int top, int assign,
                               cudaStream_t stream) {
     if (N == 0) return CW_OK;
     if (N < 0 || W <= 0 || top <= 0) return CW_ERR_BAD_SIZE;
-    return cw_launch_ordered(moe_combine_kernel, dim3(N), dim3(256), 0, stream, resid, y, sel, wt, W, top);
+    return cw_launch_ordered(moe_combine_kernel, dim3(N), dim3(256), 0, stream, resid, y, sel, wt, W, top, assign);
 }
 
 CW_TRACE_TU(grouped_gemm)

@@ -15,7 +15,7 @@
 // preemption, or when the caller supplies the tokens itself (trace replay).
 #include "common.cuh"
 
-#define CW_RS_MAX_GROUPS 8
+#define CW_RS_MAX_GROUPS 32
 
 struct StepFromStateParams {
     const int* row_slot;  // [B] state slot of each row of the step; < 0: padding

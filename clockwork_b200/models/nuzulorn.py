@@ -51,7 +51,7 @@ def _layers_2k(repeats: int) -> list:
     attention of 16 heads of 128 on 4 key/value heads over 1,024 positions with blocks of 64 pooled before them; a recurrent
     layer of 16 heads of 128 x 128; 32 experts of 1,792 in 4 groups, of which 4 of the best 2 groups (a token goes through
     7,168 rows)."""
-    moe = {"kind": "moe", "expert": {"ff": 1792}, "router": {"experts": 32, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    moe = {"kind": "moe", "expert": {"ff": 1792}, "router": {"experts": 32, "top": 4, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     capped = {"type": "attention_2", "mlp": moe, "mixer": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
                                                           "softcap": 30.0, "q_temp": {"coef": 0.1, "every": 1024}}}
     windowed = {"type": "attention", "mlp": moe, "mixer": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,

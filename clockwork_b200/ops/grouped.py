@@ -93,8 +93,10 @@ def expert_down(act: torch.Tensor, w_down: torch.Tensor, offsets: torch.Tensor, 
     return y
 
 
-def moe_combine(residual: torch.Tensor, y: torch.Tensor, sel: torch.Tensor, wt: torch.Tensor) -> None:
-    """residual[n] += sum over the choices, in order, of weight * y[n*top + choice]."""
+def moe_combine(residual: torch.Tensor, y: torch.Tensor, sel: torch.Tensor, wt: torch.Tensor, assign: bool = False) -> None:
+    """residual[n] += sum over the choices, in order, of weight * y[n*top + choice]; ``assign``: the sum replaces
+    residual[n] (zeros in rows that chose nothing)."""
     _need(residual, torch.float32, "residual", 2)
     n, w = residual.shape
-    check(library().cw_moe_combine(_ptr(residual), _ptr(y), _ptr(sel), _ptr(wt), n, w, sel.shape[1], _stream()), "moe_combine")
+    check(library().cw_moe_combine(_ptr(residual), _ptr(y), _ptr(sel), _ptr(wt), n, w, sel.shape[1], 1 if assign else 0, _stream()),
+          "moe_combine")

@@ -62,7 +62,7 @@ _SIGNATURES: dict[str, list] = {
     "cw_latent_attention_set_mma": [I],
     "cw_moe_choose": [P, P, P, P, P, I, I, I, I, I, I, P, F, I, P],
     "cw_moe_group": [P, P, P, P, I, I, P],
-    "cw_moe_combine": [P, P, P, P, I, I, I, P],
+    "cw_moe_combine": [P, P, P, P, I, I, I, I, P],
     # the delta rule, the gates and the read-out of a matrix memory (csrc/recurrence_gated.cu)
     "cw_unit_heads": [P, I, I, I, I, F, I, F, F, P],
     "cw_delta_coefficients": [P, I, P, P, P, I, I, I, I, P],

@@ -158,9 +158,10 @@ class MixtureOfExperts(FeedForward):
         y, sel, weights = self._routed(ctx, x)
         if self.shared_size:
             out = self.shared_down.to_float32(self._shared_act(x))
+            grouped_ops.moe_combine(out, y, sel, weights)  # (the rows of no request keep what the shared expert made of them)
         else:
-            out = torch.zeros((x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
-        grouped_ops.moe_combine(out, y, sel, weights)  # (the rows of no request keep what the shared expert made of them)
+            out = torch.empty((x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
+            grouped_ops.moe_combine(out, y, sel, weights, assign=True)
         return [(out, 1.0)]
 
 

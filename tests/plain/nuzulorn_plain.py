@@ -162,27 +162,42 @@ def bounded_forget_recurrence(h, w, m, eps, state=None):
 
 # ---- experts ---------------------------------------------------------------------------------------
 def route(logits, correction, top, count, keep):
-    """logits [T, E] -> (chosen experts [T, top], their sigmoid scores [T, top])."""
+    """logits [T, E] -> (chosen experts [T, top], their sigmoid scores [T, top], margins [T]: how far, in the scores that
+    rank them, the last kept group is from the first dropped one and the last chosen expert from the first one left out)."""
     T, E = logits.shape
     s = torch.sigmoid(logits)
     c = s + correction
+    margin = torch.full((T,), math.inf, dtype=logits.dtype)
     if count > 1:
         per = E // count
         grouped = c.view(T, count, per)
         rank = grouped.topk(min(2, per), dim=-1).values.sum(-1)  # [T, count]
-        kept = rank.topk(keep, dim=-1).indices
+        ordered = rank.sort(dim=-1, descending=True)
+        kept = ordered.indices[:, :keep]
+        if keep < count:
+            margin = torch.minimum(margin, ordered.values[:, keep - 1] - ordered.values[:, keep])
         allowed = torch.zeros(T, count, dtype=torch.bool)
         allowed.scatter_(1, kept, True)
         c = torch.where(allowed[:, :, None].expand(T, count, per).reshape(T, E), c, torch.full_like(c, -math.inf))
-    chosen = c.topk(top, dim=-1).indices
-    return chosen, s.gather(1, chosen)
+    ordered = c.sort(dim=-1, descending=True)
+    chosen = ordered.indices[:, :top]
+    if top < E:
+        margin = torch.minimum(margin, ordered.values[:, top - 1] - ordered.values[:, top])  # (inf when no allowed expert is left out)
+    return chosen, s.gather(1, chosen), margin
 
 
-def experts(h, w, f, router_input=exact):
-    """h [T, width] -> [T, width].  ``w``: router, correction, e<j>.gate|up|down."""
+def experts(h, w, f, log=None, routes=None):
+    """h [T, width] -> [T, width].  ``w``: router, correction, e<j>.gate|up|down.  ``log``: a list that receives (chosen,
+    margins); ``routes``: choices to use instead of this run's own (those of a run that does not round), the scores this run's."""
     r = f["router"]
     groups = r.get("groups") or {"count": 1, "keep": 1}
-    chosen, score = route(router_input(h) @ w["router"].T, w["correction"], r["top"], groups["count"], groups["keep"])
+    logits = h @ w["router"].T
+    chosen, score, margin = route(logits, w["correction"], r["top"], groups["count"], groups["keep"])
+    if log is not None:
+        log.append((chosen, margin))
+    if routes is not None:
+        chosen = routes
+        score = torch.sigmoid(logits).gather(1, chosen)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t].tolist(), score[t]):
@@ -206,18 +221,22 @@ def mixer(kind, h, w, m, eps, store=exact):
     raise ValueError(f"unknown layer type {kind!r}")
 
 
-def forward(config, weights, tokens, dtype=torch.float64, act=exact, store=exact, return_layers=False):
-    """Logits [T, vocab] of one sequence (and, if asked, the residual rows behind every layer after and before the depth average).  ``act``: applied
-    to what a bfloat16 run keeps in bfloat16 between kernels (normed rows); ``store``: to what the cache keeps."""
+def forward(config, weights, tokens, dtype=torch.float64, act=exact, store=exact, return_layers=False, log=None, routes=None):
+    """Logits [T, vocab] of one sequence (and, if asked, the residual rows behind every layer after and before the average
+    over the depth).  ``act``: applied to what a bfloat16 run keeps in bfloat16 between kernels (normed rows); ``store``: to
+    what the cache keeps.  ``log``: receives every feed-forward's (chosen experts, margins), in layer order; ``routes``: such
+    a log of another run, whose choices this run uses."""
     w = {k: v.to(dtype) for k, v in weights.items()}
     eps, mult = config["norm"]["eps"], config["residual_mult"]
     x = input_rows(tokens, w["embed"], w["bigram"], config["embedding"]["bigram"])
     history, layer_out, averaged = [x], [], []
+    routes = list(routes) if routes is not None else None
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}"
         y = x + mult * mixer(layer["type"], act(unit_rms(x, eps) * w[f"{p}.norm1"]), sub(w, f"{p}.mix"), layer["mixer"], eps, store)
         if layer.get("mlp") is not None:
-            y = y + mult * experts(act(unit_rms(y, eps) * w[f"{p}.norm2"]), sub(w, f"{p}.mlp"), layer["mlp"])
+            y = y + mult * experts(act(unit_rms(y, eps) * w[f"{p}.norm2"]), sub(w, f"{p}.mlp"), layer["mlp"], log,
+                                   routes.pop(0)[0] if routes is not None else None)
         layer_out.append(y)
         history.append(y)
         x = sum(c * X for c, X in zip(w[f"{p}.dwa"], history))
