@@ -526,16 +526,41 @@ depth_average_kernel(const float* x, const float* __restrict__ a, const float* _
     pdl_wait();
     const size_t at = (size_t)blockIdx.x * W;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float y = x[at + c];
-        if (a != nullptr) y = fmaf(ca, a[at + c], y);
-        if (b != nullptr) y = fmaf(cb, b[at + c], y);
-        history[(size_t)index * plane + at + c] = y;
-        float acc = 0.f;
-        for (int j = 0; j < index; ++j) acc = fmaf(coef[j], history[(size_t)j * plane + at + c], acc);
-        acc = fmaf(coef[index], y, acc);
-        next[at + c] = acc;
-        ss = fmaf(acc, acc, ss);
+    if ((W & 3) == 0 && (plane & 3) == 0) {  // four columns a thread, 16-byte accesses (every pointer is a tensor's start or a plane's)
+        for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+            float4 y = *(const float4*)(x + at + c);
+            if (a != nullptr) {
+                const float4 t = *(const float4*)(a + at + c);
+                y.x = fmaf(ca, t.x, y.x); y.y = fmaf(ca, t.y, y.y); y.z = fmaf(ca, t.z, y.z); y.w = fmaf(ca, t.w, y.w);
+            }
+            if (b != nullptr) {
+                const float4 t = *(const float4*)(b + at + c);
+                y.x = fmaf(cb, t.x, y.x); y.y = fmaf(cb, t.y, y.y); y.z = fmaf(cb, t.z, y.z); y.w = fmaf(cb, t.w, y.w);
+            }
+            *(float4*)(history + (size_t)index * plane + at + c) = y;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < index; ++j) {
+                const float k = coef[j];
+                const float4 t = *(const float4*)(history + (size_t)j * plane + at + c);
+                acc.x = fmaf(k, t.x, acc.x); acc.y = fmaf(k, t.y, acc.y); acc.z = fmaf(k, t.z, acc.z); acc.w = fmaf(k, t.w, acc.w);
+            }
+            const float k = coef[index];
+            acc.x = fmaf(k, y.x, acc.x); acc.y = fmaf(k, y.y, acc.y); acc.z = fmaf(k, y.z, acc.z); acc.w = fmaf(k, y.w, acc.w);
+            *(float4*)(next + at + c) = acc;
+            ss = fmaf(acc.x, acc.x, fmaf(acc.y, acc.y, fmaf(acc.z, acc.z, fmaf(acc.w, acc.w, ss))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < W; c += blockDim.x) {
+            float y = x[at + c];
+            if (a != nullptr) y = fmaf(ca, a[at + c], y);
+            if (b != nullptr) y = fmaf(cb, b[at + c], y);
+            history[(size_t)index * plane + at + c] = y;
+            float acc = 0.f;
+            for (int j = 0; j < index; ++j) acc = fmaf(coef[j], history[(size_t)j * plane + at + c], acc);
+            acc = fmaf(coef[index], y, acc);
+            next[at + c] = acc;
+            ss = fmaf(acc, acc, ss);
+        }
     }
     if (w == nullptr) return;
     ss = block_sum(ss, scratch);

@@ -128,7 +128,7 @@ extern "C" int cw_rotate_store(const float* src, int ld, const int* positions, c
 }
 
 // ---- the means of whole blocks of positions -----------------------------------------------------------------
-// A block per token.  A token at position p with (p + 1) % pool == 0 ends the block of positions p - pool + 1 .. p: the
+// A thread block per (token, 256 columns of its rows).  A token at position p with (p + 1) % pool == 0 ends the block of positions p - pool + 1 .. p: the
 // mean of those positions' cache rows [G, dk + dv] (summed in float32 in the order of the positions, divided by pool, rounded
 // once) goes to row pool_slots[n] of the second cache.  The positions' rows are in the cache when the kernel runs: the
 // step's own tokens were stored before, and the cache manager keeps at least the last `pool` positions of a request.
@@ -149,21 +149,39 @@ pool_rows_kernel(const T* __restrict__ cache, const int* __restrict__ block_tabl
         if (threadIdx.x == 0) cw_report(status, CW_ST_SLOT_RANGE, n, slot);
         return;
     }
+    __shared__ int rows[64];  // the cache rows of up to 64 positions of the block at a time (-1: none)
     const int* table = block_tables + (size_t)seq * max_blocks;
     const float inv = 1.0f / (float)pool;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float sum = 0.f;
-        for (int j = p - pool + 1; j <= p; ++j) {
-            const int blk = j / page_size;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    float sum = 0.f;
+    for (int j0 = p - pool + 1; j0 <= p; j0 += 64) {
+        const int count = min(64, p + 1 - j0);
+        __syncthreads();  // the rows before are used up
+        for (int i = threadIdx.x; i < count; i += blockDim.x) {
+            const int j = j0 + i, blk = j / page_size;
             const int page = blk < max_blocks ? table[blk] : -1;
             if (page < 0 || page >= num_pages) {
-                if (c == 0) cw_report(status, CW_ST_PAGE_RANGE, n, page);
-                continue;
+                if (blockIdx.y == 0) cw_report(status, CW_ST_PAGE_RANGE, n, page);
+                rows[i] = -1;
+            } else {
+                rows[i] = page * page_size + j % page_size;
             }
-            sum += to_f(cache[((size_t)page * page_size + j % page_size) * width + c]);
         }
-        pool_cache[(size_t)slot * width + c] = from_f<T>(sum * inv);
+        __syncthreads();
+        if (c >= width) continue;
+        // sixteen positions at a time: their loads are in flight together, the sum keeps the positions' order
+        for (int i0 = 0; i0 < count; i0 += 16) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int row = i0 + i < count ? rows[i0 + i] : -1;
+                v[i] = row >= 0 ? to_f(cache[(size_t)row * width + c]) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sum += v[i];
+        }
     }
+    if (c < width) pool_cache[(size_t)slot * width + c] = from_f<T>(sum * inv);
 }
 
 extern "C" int cw_pool_rows(const void* cache, const int* block_tables, int max_blocks, int page_size, int num_pages,
@@ -173,11 +191,13 @@ extern "C" int cw_pool_rows(const void* cache, const int* block_tables, int max_
     if (N < 0 || width <= 0 || pool <= 0 || page_size <= 0 || max_blocks <= 0 || pool_rows <= 0) return CW_ERR_BAD_SIZE;
     int threads = 32;
     while (threads < 256 && threads < width) threads *= 2;
+    const dim3 grid(N, (width + threads - 1) / threads);
+    if (grid.y > 65535) return CW_ERR_UNSUPPORTED;
     if (dtype == 0)
-        return cw_launch_ordered(pool_rows_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float*)cache, block_tables, max_blocks,
+        return cw_launch_ordered(pool_rows_kernel<float>, grid, dim3(threads), 0, stream, (const float*)cache, block_tables, max_blocks,
                                  page_size, num_pages, positions, tok_seq, pool_slots, (float*)pool_cache, pool_rows, width, pool, status);
     if (dtype == 1)
-        return cw_launch_ordered(pool_rows_kernel<bf16>, dim3(N), dim3(threads), 0, stream, (const bf16*)cache, block_tables, max_blocks,
+        return cw_launch_ordered(pool_rows_kernel<bf16>, grid, dim3(threads), 0, stream, (const bf16*)cache, block_tables, max_blocks,
                                  page_size, num_pages, positions, tok_seq, pool_slots, (bf16*)pool_cache, pool_rows, width, pool, status);
     return CW_ERR_BAD_DTYPE;
 }
