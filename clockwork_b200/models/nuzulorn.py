@@ -135,7 +135,7 @@ class NuzulornArchitecture:
         layers = [LayerSpec(block="depth_averaged_residual", mixer=mixer, ffn=ffn, mixer_norm=norm, ffn_norm=norm, prefix=f"l{i}",
                             block_params={"residual_mult": config.residual_mult, "run": i})
                   for i, (mixer, ffn) in enumerate(config.layers)]
-        pair = PartSpec("hashed_pair", dict(config.pair, size=config.width, name="bigram"))
+        pair = PartSpec("hashed_pair", dict(config.pair, size=config.width, name="bigram", vocab=config.vocab))
         return ModelSpec(architecture=self.name, vocab_size=config.vocab, hidden_size=config.width, layers=layers,
                          schedule=sequential_schedule(len(layers)), final_norm=norm, embedding_name="embed",
                          final_norm_prefix="final.norm", head_name="head", tie_word_embeddings=True,

@@ -167,7 +167,8 @@ def sum_rmsnorm_add(resid: torch.Tensor, terms, weight: torch.Tensor, eps: float
           "sum_rmsnorm_add")
 
 
-def pair_embed_add(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, ctx, view, mul_prev: int, mul_cur: int) -> None:
+def pair_embed_add(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, ctx, view, mul_prev: int, mul_cur: int,
+                   vocab: int = 1 << 30) -> None:
     """In place on float32 ``x`` [N, W]: row ``(previous token * mul_prev + token * mul_cur) mod buckets`` of ``table``
     [buckets + 1, W] is added to every token's row; a request's first token (position 0) reads the last row.  The token
     before a portion's first one comes from the request's state (``view``: int32 [slots, 1]), where the portion's last
@@ -182,7 +183,7 @@ def pair_embed_add(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, ctx,
         raise ValueError(f"table {tuple(table.shape)} does not fit rows of {w}")
     check(library().cw_pair_embed_add(_ptr(x), _ptr(table), _ptr(ids), _ptr(ctx.positions), _ptr(ctx.tok_seq), _ptr(ctx.q_start),
                                       _ptr(view.state), view.state.stride(0), _ptr(view.slots), table.shape[0] - 1, int(mul_prev),
-                                      int(mul_cur), n, ctx.num_seqs, w, 1 << 30, dtype_code(table.dtype), _ptr(ctx.status), _stream()),
+                                      int(mul_cur), n, ctx.num_seqs, w, int(vocab), dtype_code(table.dtype), _ptr(ctx.status), _stream()),
           "pair_embed_add")
 
 

@@ -91,16 +91,19 @@ def pool_rows(cache_rows: torch.Tensor, block_tables: torch.Tensor, positions: t
                                  width, int(pool), n, dtype_code(cache_rows.dtype), _ptr(status), _stream()), "pool_rows")
 
 
-def window_parts(num_tokens: int, window: int, dtype: torch.dtype) -> int:
+def window_parts(num_tokens: int, window: int, dtype: torch.dtype, longest_context: int | None = None) -> int:
     """In how many pieces the keys of a row are cut (the pieces are added up by a second kernel).  float32 runs never
     cut: their results do not depend on the step's size to the last bit.  bfloat16: finely when a step has so few
     tokens that whole windows per thread block would leave most of the GPU idle; coarsely in longer steps over long
-    windows, where the last rows of a prompt would otherwise run several times as long as the first."""
+    windows, where the last rows of a prompt would otherwise run several times as long as the first.
+    ``longest_context``: a bound on the step's longest context, for windows that never close."""
     if dtype != torch.bfloat16 or window <= 256:
         return 1
     if num_tokens < SPLIT_BELOW_TOKENS:
         return max(1, min(SPLIT_MAX_PARTS, window // 128, 128 // max(1, num_tokens)))
     longest = min(window, num_tokens + window // 2)  # (keys that a row of this step may see: a guess, contexts are not known here)
+    if window >= NO_WINDOW and longest_context is not None:
+        longest = max(num_tokens, longest_context)
     return max(1, min(longest // SPLIT_LONG_KEYS, SPLIT_MAX_ROW_PARTS // num_tokens, SPLIT_MAX_PARTS))
 
 

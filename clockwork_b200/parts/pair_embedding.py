@@ -1,7 +1,8 @@
 """An embedding part that adds, to every token's embedding row, a row of a second table chosen by a hash of the pair
 (previous token, token).
 
-Parameters: ``size`` (the rows' width), ``buckets``, ``mul_prev``, ``mul_cur``, ``name`` (the tensor's name).  The table has
+Parameters: ``size`` (the rows' width), ``buckets``, ``mul_prev``, ``mul_cur``, ``name`` (the tensor's name), optionally
+``vocab`` (token ids at or above it are reported and skipped).  The table has
 ``buckets + 1`` rows: token t reads row ``(token_(t-1) * mul_prev + token_t * mul_cur) mod buckets``, a request's first token
 the last row.  The previous token is part of a request's state: the part asks the cache manager for one int32 per request
 (``SlotStateNeed``), where the last token of a prompt portion (or a decoded token) stays for the step that follows; inside a
@@ -28,6 +29,7 @@ class HashedPairEmbedding(Part):
         self.size, self.buckets = int(p["size"]), int(p["buckets"])
         self.mul_prev, self.mul_cur = int(p["mul_prev"]), int(p["mul_cur"])
         self.table_name = str(p["name"])
+        self.vocab = int(p.get("vocab") or (1 << 30))
         if self.buckets < 1 or self.mul_prev < 0 or self.mul_cur < 0:
             raise ValueError("buckets must be positive and the multipliers non-negative")
         self.table: torch.Tensor | None = None
@@ -42,7 +44,7 @@ class HashedPairEmbedding(Part):
         self.table = fetch(self.table_name)
 
     def add_to_embedding(self, ctx: StepContext, x: torch.Tensor, token_ids: torch.Tensor, view: StateView) -> None:
-        ops.pair_embed_add(x, self.table, token_ids, ctx, view, self.mul_prev, self.mul_cur)
+        ops.pair_embed_add(x, self.table, token_ids, ctx, view, self.mul_prev, self.mul_cur, self.vocab)
 
 
 register_embedding("hashed_pair", HashedPairEmbedding, replace=True)

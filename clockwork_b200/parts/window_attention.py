@@ -191,7 +191,7 @@ class WindowAttention(Mixer):
                 window_ops.store_rows(q, self.heads * self.dim, self.kv_heads * self.row, rows, view.slots, ctx.status)
         if self.pool and view.write:
             window_ops.pool_rows(rows, view.block_tables, ctx.positions, ctx.tok_seq, pooled.slots, pooled.k_cache, self.pool, ctx.status)
-        parts = window_ops.window_parts(ctx.num_tokens, self.window, self.dtype)
+        parts = window_ops.window_parts(ctx.num_tokens, self.window, self.dtype, ctx.max_ctx_len)
         return window_ops.window_attention(q, rows, view.block_tables, ctx.positions, ctx.tok_seq, ctx.q_start, self.heads, self.kv_heads,
                                            self.dim, self.vdim, self.window, self.scale, self.head_scale, self.talk,
                                            self.head_bias, self.weights == "sigmoid", ctx.status, parts,
