@@ -64,7 +64,7 @@ CONFIG_C = _model(120, 72, 1e-5, 0.3, (211, 5, 11), [
     (_recurrent(5, 8, 24), None),
     (_window(6, 1, 8, 24, 0.35, 16, 4, 4, 300.0), _moe(28, 8, 3, 2.5, (4, 2))),
     (_capped(6, 1, 8, 24, 0.35, 8.0, 0.5, 16), _moe(48, 2, 1, 0.5, (2, 1))),
-    (_window(2, 2, 40, 8, 0.15, 5, 12, 40, 1000000.0), _moe(12, 6, 6, 1.0, (3, 3))),
+    (_window(2, 2, 40, 8, 0.15, 5, 11, 40, 200000.0), _moe(12, 6, 6, 1.0, (3, 3))),
 ])
 CONFIG_D = _model(1000, 320, 1e-6, 0.5, (1201, 97, 29), [  # sizes that the tensor-core kernels take
     (_capped(8, 2, 32, 64, 32 ** -0.5, 15.0, 0.7, 32), _moe(128, 8, 2, 1.7, (4, 2))),
