@@ -22,7 +22,7 @@ from clockwork_b200 import EngineConfig, ops
 from clockwork_b200.config import PartSpec
 from clockwork_b200.engine import LLMEngine
 from clockwork_b200.engine.trace import TraceSession
-from clockwork_b200.parts import StateView, build_part
+from clockwork_b200.parts import build_part
 from clockwork_b200.sampling import SamplingParams
 from clockwork_b200.weights.loader import make_fetch
 from tests.gpu_tools import DEV, PartHarness
